@@ -1,0 +1,107 @@
+"""GPU parity of the scaled architecture (LayerNorm, causal softmax attention, GELU MLP, tied
+head) against the CPU oracle: BF16 mode within 1e-2, FP32 check mode within 1e-5, on the
+BASELINE configuration "CPU reference step": 4 layers, d_model 256, 4 heads, ctx 256, batch 8,
+bytes uniform from seed 0, weights N(0, 0.02) from seed 1, one AdamW step."""
+import numpy as np
+import pytest
+import torch
+
+from oracle.model import Arch, Model, specification
+from oracle.optim import Hyper, Optimizer
+from turbogpt_b200 import Config, ConfigEx, Native
+from turbogpt_b200 import bridge
+from helpers import max_relative, relative
+
+pytestmark = pytest.mark.gpu
+
+
+def fixture(depth, width, heads, context, batch, fp32):
+    torch.set_num_threads(8)
+    rng = np.random.default_rng(0)
+    stream = rng.integers(0, 256, batch * context + 1, dtype=np.uint8)
+    x = np.stack([stream[b * context:(b + 1) * context] for b in range(batch)])
+    y = np.stack([stream[b * context + 1:(b + 1) * context + 1] for b in range(batch)])
+    arch = Arch.gpt(depth, width, heads)
+    model = Model(arch, seed=1, scale=.02, fp32=fp32)
+    wrng = np.random.default_rng(1)
+    w = model.flat()
+    offset = 0
+    for name, shape in specification(arch):  # weights N(0, 0.02) from seed 1; norms keep 1 / 0
+        n = int(np.prod(shape))
+        if len(shape) == 2:
+            w[offset:offset + n] = (wrng.standard_normal(n) * .02).astype(np.float32)
+        offset += n
+    model.load(w)
+    return arch, model, w, x, y
+
+
+@pytest.mark.parametrize("fp32,flags", [(False, 0), (False, bridge.FLAG_NO_TENSOR_CORES), (True, 0)])
+def test_step_parity(fp32, flags):
+    depth, width, heads, context, batch = 4, 256, 4, 256, 8
+    arch, model, w, x, y = fixture(depth, width, heads, context, batch, fp32)
+    base = Config(depth=depth, context=context, batch=batch, learning_rate=3e-4, beta1=.9, beta2=.95,
+                  weight_decay=.1, clip=0)
+    ex = ConfigEx.gpt(base, width, heads, precision=bridge.PRECISION_FP32 if fp32 else bridge.PRECISION_BF16,
+                      flags=flags)
+    target, expected_grad, expected_losses = model.batch(x, y)
+    tolerance = 1e-5 if fp32 else 1e-2
+    with Native(ex) as engine:
+        engine.set_weights(w)
+        logits, gradients, losses = engine.batch(x, y)
+        # per-op max relative error (relative to the largest magnitude of the tensor)
+        assert max_relative(logits, target) <= tolerance
+        np.testing.assert_allclose(losses, expected_losses, rtol=tolerance, atol=tolerance)
+        offset = 0
+        for name, param in model.params.items():
+            n = param.numel()
+            assert max_relative(gradients[offset:offset + n], expected_grad[offset:offset + n]) <= \
+                (3e-5 if fp32 else 2.5e-2), name
+            offset += n
+        assert relative(gradients, expected_grad) <= tolerance
+        # one AdamW step on the oracle's gradient: the update itself is FP32 in both modes
+        opt = Optimizer(arch, Hyper(learning_rate=3e-4, beta1=.9, beta2=.95, weight_decay=.1, clip=0), w,
+                        hidden="adamw")
+        opt.step(expected_grad)
+        engine.optimizer_test(expected_grad, 1)
+        np.testing.assert_allclose(engine.weights(), opt.w, atol=2e-6, rtol=2e-5)
+
+
+def test_small_ragged_shapes_fp32():
+    """Widths and contexts off the tensor-core tile sizes, FP32 check mode."""
+    for depth, width, heads, context, batch in [(2, 64, 2, 24, 3), (1, 96, 3, 40, 5)]:
+        arch, model, w, x, y = fixture(depth, width, heads, context, batch, True)
+        ex = ConfigEx.gpt(Config(depth=depth, context=context, batch=batch, clip=0), width, heads,
+                          precision=bridge.PRECISION_FP32)
+        target, expected_grad, expected_losses = model.batch(x, y)
+        with Native(ex) as engine:
+            engine.set_weights(w)
+            logits, gradients, losses = engine.batch(x, y)
+        assert max_relative(logits, target) <= 1e-5
+        assert relative(gradients, expected_grad) <= 1e-5
+        np.testing.assert_allclose(losses, expected_losses, rtol=1e-5, atol=1e-5)
+
+
+def test_training_loss_curve_follows_oracle():
+    """A short BF16 training run on seeded bytes: per-step mean loss within 1% of the CPU oracle
+    driving the same sampled bytes and its own AdamW."""
+    from oracle import indexing
+    depth, width, heads, context, batch, steps = 2, 128, 2, 64, 8, 12
+    arch, model, w, _, _ = fixture(depth, width, heads, context, batch, False)
+    data = np.random.default_rng(3).integers(0, 64, 1 << 14, dtype=np.uint8)
+    hyper = Hyper(learning_rate=1e-3, beta1=.9, beta2=.95, weight_decay=.1, clip=1.0)
+    opt = Optimizer(arch, hyper, w, hidden="adamw")
+    expected = []
+    for step in range(steps):
+        model.load(opt.w)
+        x, y = indexing.byte_batch(data, 3407, step, batch, context)
+        _, grad, losses = model.batch(x, y)
+        expected.append(losses.mean())
+        opt.step(grad)
+    base = Config(depth=depth, context=context, batch=batch, learning_rate=1e-3, clip=1.0)
+    with Native(ConfigEx.gpt(base, width, heads)) as engine:
+        engine.set_weights(w)
+        engine.set_data(data)
+        engine.train(steps)
+        actual = engine.training_losses(steps).mean(1)
+    np.testing.assert_allclose(actual, np.array(expected), rtol=.01)
+    assert actual[-1] < actual[0]

@@ -1,0 +1,470 @@
+// HBM-bound kernels of the step: byte sampling, embedding gather/scatter, norms, rotation,
+// MLP activations, softmax cross-entropy, loss history.  Each is one pass over its operands
+// with 128-bit accesses; rows are handled by one warp so the row statistics are shuffle
+// reductions.
+#include "device_utils.cuh"
+#include "kernels.cuh"
+
+#define DISPATCH(t, ...)                                                                                    \
+    do {                                                                                                    \
+        if ((t) == Dtype::BF16) {                                                                           \
+            using T = bf16;                                                                                 \
+            __VA_ARGS__;                                                                                    \
+        } else {                                                                                            \
+            using T = float;                                                                                \
+            __VA_ARGS__;                                                                                    \
+        }                                                                                                   \
+    } while (0)
+
+static inline int blocks_for(int64_t items, int per_block, int64_t cap = 1 << 30) {
+    int64_t b = (items + per_block - 1) / per_block;
+    return int(b < 1 ? 1 : (b > cap ? cap : b));
+}
+
+// ------------------------------------------------------------------------------------------
+// Byte sampling: one block per sequence.  endpoint = lo + hash(seed + step*B_global + s_global)
+// % (size - lo), lo = max(8, context); x = data[e-ctx .. e), y = data[e-ctx+1 .. e].
+// ------------------------------------------------------------------------------------------
+__global__ void sample_kernel(SampleArgs a) {
+    __shared__ long long endpoint;
+    const int sequence = blockIdx.x;
+    if (threadIdx.x == 0) {
+        const uint64_t step = a.fixed_step >= 0 ? uint64_t(a.fixed_step) : uint64_t(a.counters->step);
+        const int64_t lo = a.context > 8 ? a.context : 8;
+        const uint64_t global_batch = uint64_t(a.batch) * uint64_t(a.world);
+        const uint64_t global_sequence = uint64_t(a.rank) * uint64_t(a.batch) + uint64_t(sequence);
+        endpoint = lo + (long long)(hash_u64(a.seed + step * global_batch + global_sequence) %
+                                    uint64_t(a.size - lo));
+    }
+    __syncthreads();
+    const uint8_t *source = a.data + endpoint - a.context;
+    for (int p = threadIdx.x; p < a.context; p += blockDim.x) {
+        a.x[int64_t(sequence) * a.context + p] = source[p];
+        a.y[int64_t(sequence) * a.context + p] = source[p + 1];
+    }
+}
+void launch_sample(const SampleArgs &a, cudaStream_t s) {
+    sample_kernel<<<a.batch, 128, 0, s>>>(a);
+}
+
+template <class T>
+__global__ void embedding_kernel(const T *__restrict__ table, const uint8_t *__restrict__ x, T *__restrict__ hidden,
+                                 int64_t vectors, int width8) {
+    for (int64_t i = blockIdx.x * int64_t(blockDim.x) + threadIdx.x; i < vectors;
+         i += int64_t(gridDim.x) * blockDim.x) {
+        int64_t token = i / width8;
+        int c = int(i % width8) * 8;
+        float v[8];
+        load8(table + int64_t(x[token]) * width8 * 8 + c, v);
+        store8(hidden + token * width8 * 8 + c, v);
+    }
+}
+void launch_embedding(Dtype t, const void *table, const uint8_t *x, void *hidden, int tokens, int width,
+                      cudaStream_t s) {
+    int64_t vectors = int64_t(tokens) * (width / 8);
+    DISPATCH(t, (embedding_kernel<T><<<blocks_for(vectors, 256, 148 * 16), 256, 0, s>>>(
+                    (const T *)table, x, (T *)hidden, vectors, width / 8)));
+}
+
+// One block per byte value; each warp owns a slice of columns and scans all tokens in order,
+// so the FP32 sums have a fixed order (the reference uses atomicAdd, cuda/model.cuh:96-97).
+template <class T>
+__global__ void embedding_backward_kernel(const T *__restrict__ dhidden, const uint8_t *__restrict__ x,
+                                          float *__restrict__ grad, int tokens, int width, bool accumulate) {
+    const int value = blockIdx.x, lane = threadIdx.x % 32, warp = threadIdx.x / 32, warps = blockDim.x / 32;
+    for (int c0 = warp * 32; c0 < width; c0 += warps * 32) {
+        const int c = c0 + lane;
+        float sum = 0;
+        for (int t0 = 0; t0 < tokens; t0 += 32) {
+            int t = t0 + lane;
+            unsigned hits = __ballot_sync(0xffffffffu, t < tokens && x[t] == value);
+            while (hits) {
+                int bit = __ffs(hits) - 1;
+                hits &= hits - 1;
+                if (c < width)
+                    sum += to_float(dhidden[int64_t(t0 + bit) * width + c]);
+            }
+        }
+        if (c < width) {
+            float *out = grad + int64_t(value) * width + c;
+            *out = accumulate ? *out + sum : sum;
+        }
+    }
+}
+void launch_embedding_backward(Dtype t, const void *dhidden, const uint8_t *x, float *grad, int tokens,
+                               int width, bool accumulate, cudaStream_t s) {
+    int threads = width >= 256 ? 256 : (width + 31) / 32 * 32;
+    DISPATCH(t, (embedding_backward_kernel<T><<<Vocabulary, threads, 0, s>>>((const T *)dhidden, x, grad, tokens,
+                                                                           width, accumulate)));
+}
+
+// ------------------------------------------------------------------------------------------
+// Norms.  RMSNorm: y = x * rsqrt(mean(x^2) + 1e-6) * w.  LayerNorm: y = (x - mean) *
+// rsqrt(var + 1e-5) * w + b.  FP32 math on FP32 master scales, one rounding to the activation
+// type at the end.
+// ------------------------------------------------------------------------------------------
+__device__ __forceinline__ void load_scale8(const bf16 *high, const uint16_t *low, int c, float (&w)[8]) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+        w[j] = join_weight(high[c + j], low[c + j]);
+}
+template <class T>
+__device__ __forceinline__ void row_statistics(int kind, const T *row, int width, int lane, float &mean,
+                                               float &inv) {
+    float sum = 0, squares = 0;
+    for (int c = lane * 8; c < width; c += 256) {
+        float v[8];
+        load8(row + c, v);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            sum += v[j];
+            squares += v[j] * v[j];
+        }
+    }
+    if (kind == TG_NORM_RMS) {
+        mean = 0;
+        inv = rsqrtf(warp_sum(squares) / width + 1e-6f);
+        return;
+    }
+    mean = warp_sum(sum) / width;
+    float centred = 0;
+    for (int c = lane * 8; c < width; c += 256) {
+        float v[8];
+        load8(row + c, v);
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+            centred += (v[j] - mean) * (v[j] - mean);
+    }
+    inv = rsqrtf(warp_sum(centred) / width + 1e-5f);
+}
+template <class T> __global__ void __launch_bounds__(256) norm_kernel(NormArgs a) {
+    const int lane = threadIdx.x % 32;
+    const int row = blockIdx.x * (blockDim.x / 32) + threadIdx.x / 32;
+    if (row >= a.rows)
+        return;
+    const T *x = (const T *)a.x + int64_t(row) * a.width;
+    T *y = (T *)a.y + int64_t(row) * a.width;
+    float mean, inv;
+    row_statistics(a.kind, x, a.width, lane, mean, inv);
+    for (int c = lane * 8; c < a.width; c += 256) {
+        float v[8], w[8], out[8];
+        load8(x + c, v);
+        load_scale8(a.scale_high, a.scale_low, c, w);
+        if (a.kind == TG_NORM_RMS) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                out[j] = v[j] * inv * w[j];
+        } else {
+            float b[8];
+            load_scale8(a.bias_high, a.bias_low, c, b);
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                out[j] = (v[j] - mean) * inv * w[j] + b[j];
+        }
+        store8(y + c, out);
+    }
+}
+void launch_norm(Dtype t, const NormArgs &a, cudaStream_t s) {
+    DISPATCH(t, (norm_kernel<T><<<blocks_for(a.rows, 8), 256, 0, s>>>(a)));
+}
+
+// dx = (dz - [mean(dz)] - z * mean(dz * z)) * inv with dz = dy * w, z the normalised input;
+// rounded to the activation type, then added to the running residual gradient with a second
+// rounding (reference cuda/ops.cuh:67-80).  Scale/bias gradients: shared-memory sums per block,
+// then a fixed-order sum over blocks.
+template <class T> __global__ void __launch_bounds__(256) norm_backward_kernel(NormBackwardArgs a) {
+    extern __shared__ float sums[]; // [2][width]
+    const int lane = threadIdx.x % 32, warps = blockDim.x / 32;
+    for (int c = threadIdx.x; c < 2 * a.width; c += blockDim.x)
+        sums[c] = 0;
+    __syncthreads();
+    for (int row = blockIdx.x * warps + threadIdx.x / 32; row < a.rows; row += gridDim.x * warps) {
+        const T *x = (const T *)a.x + int64_t(row) * a.width;
+        const T *dy = (const T *)a.dy + int64_t(row) * a.width;
+        float mean, inv;
+        row_statistics(a.kind, x, a.width, lane, mean, inv);
+        float sum_dz = 0, sum_dzz = 0;
+        for (int c = lane * 8; c < a.width; c += 256) {
+            float v[8], g[8], w[8];
+            load8(x + c, v);
+            load8(dy + c, g);
+            load_scale8(a.scale_high, a.scale_low, c, w);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                float z = (v[j] - mean) * inv, dz = g[j] * w[j];
+                sum_dz += dz;
+                sum_dzz += dz * z;
+                atomicAdd(&sums[c + j], g[j] * z);
+                if (a.kind == TG_NORM_LAYER)
+                    atomicAdd(&sums[a.width + c + j], g[j]);
+            }
+        }
+        sum_dzz = warp_sum(sum_dzz) / a.width;
+        sum_dz = a.kind == TG_NORM_LAYER ? warp_sum(sum_dz) / a.width : 0.f;
+        for (int c = lane * 8; c < a.width; c += 256) {
+            float v[8], g[8], w[8], out[8];
+            load8(x + c, v);
+            load8(dy + c, g);
+            load_scale8(a.scale_high, a.scale_low, c, w);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                float z = (v[j] - mean) * inv, dz = g[j] * w[j];
+                out[j] = (dz - sum_dz - z * sum_dzz) * inv;
+            }
+            if (a.residual_in) {
+                float r[8];
+                load8((const T *)a.residual_in + int64_t(row) * a.width + c, r);
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                    out[j] = r[j] + rounded<T>(out[j]);
+            }
+            store8((T *)a.dx + int64_t(row) * a.width + c, out);
+        }
+    }
+    __syncthreads();
+    for (int c = threadIdx.x; c < 2 * a.width; c += blockDim.x)
+        a.partial[int64_t(blockIdx.x) * 2 * a.width + c] = sums[c];
+}
+__global__ void norm_backward_reduce_kernel(const float *partial, float *dscale, float *dbias, int width,
+                                            int blocks) {
+    int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= 2 * width || (c >= width && !dbias))
+        return;
+    float sum = 0;
+    for (int b = 0; b < blocks; ++b)
+        sum += partial[int64_t(b) * 2 * width + c];
+    if (c < width)
+        dscale[c] = sum;
+    else
+        dbias[c - width] = sum;
+}
+int norm_backward_blocks(int rows, int sms) {
+    return blocks_for(rows, 8, int64_t(sms) * 2);
+}
+void launch_norm_backward(Dtype t, const NormBackwardArgs &a, cudaStream_t s) {
+    size_t shared = size_t(2) * a.width * sizeof(float);
+    DISPATCH(t, {
+        if (shared > 48 * 1024)
+            CHECK_CUDA(cudaFuncSetAttribute(norm_backward_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                            int(shared)));
+        norm_backward_kernel<T><<<a.blocks, 256, shared, s>>>(a);
+    });
+    norm_backward_reduce_kernel<<<blocks_for(2 * a.width, 128), 128, 0, s>>>(a.partial, a.dscale, a.dbias, a.width,
+                                                                           a.blocks);
+}
+
+// ------------------------------------------------------------------------------------------
+// Partial rotary embedding: dims (0, 1) of every query and key head turn `position` radians.
+// Products are kept unfused so the rounding matches the PyTorch model.
+// ------------------------------------------------------------------------------------------
+template <class T>
+__global__ void rope_kernel(T *qkv, int64_t pairs, int context, int width, int heads, bool inverse) {
+    int64_t i = blockIdx.x * int64_t(blockDim.x) + threadIdx.x;
+    if (i >= pairs)
+        return;
+    const int d_head = width / heads;
+    int64_t token = i / (2 * heads);
+    int slot = int(i % (2 * heads)); // query heads, then key heads
+    int position = int(token % context);
+    T *pair = qkv + token * 3 * width + (slot / heads) * width + (slot % heads) * d_head;
+    float x = to_float(pair[0]), y = to_float(pair[1]);
+    float c = float(cos(double(position))), sn = float(sin(double(position)));
+    if (inverse)
+        sn = -sn;
+    pair[0] = from_float<T>(__fsub_rn(__fmul_rn(x, c), __fmul_rn(y, sn)));
+    pair[1] = from_float<T>(__fadd_rn(__fmul_rn(x, sn), __fmul_rn(y, c)));
+}
+void launch_rope(Dtype t, void *qkv, int tokens, int context, int width, int heads, bool inverse,
+                 cudaStream_t s) {
+    int64_t pairs = int64_t(tokens) * 2 * heads;
+    DISPATCH(t, (rope_kernel<T><<<blocks_for(pairs, 256), 256, 0, s>>>((T *)qkv, pairs, context, width, heads,
+                                                                      inverse)));
+}
+
+// ------------------------------------------------------------------------------------------
+// MLP activations with the forward's roundings: act = round(g * sigmoid(g)); out = round(act * u).
+// ------------------------------------------------------------------------------------------
+template <class T>
+__global__ void swiglu_kernel(const T *__restrict__ wide, T *__restrict__ out, int64_t vectors, int hidden8) {
+    for (int64_t i = blockIdx.x * int64_t(blockDim.x) + threadIdx.x; i < vectors;
+         i += int64_t(gridDim.x) * blockDim.x) {
+        int64_t token = i / hidden8;
+        int c = int(i % hidden8) * 8;
+        float g[8], u[8], r[8];
+        load8(wide + token * hidden8 * 16 + c, g);
+        load8(wide + token * hidden8 * 16 + hidden8 * 8 + c, u);
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+            r[j] = rounded<T>(g[j] * sigmoid(g[j])) * u[j];
+        store8(out + token * hidden8 * 8 + c, r);
+    }
+}
+void launch_swiglu(Dtype t, const void *wide, void *out, int tokens, int hidden, cudaStream_t s) {
+    int64_t vectors = int64_t(tokens) * (hidden / 8);
+    DISPATCH(t, (swiglu_kernel<T><<<blocks_for(vectors, 256, 148 * 16), 256, 0, s>>>((const T *)wide, (T *)out,
+                                                                                 vectors, hidden / 8)));
+}
+template <class T>
+__global__ void swiglu_backward_kernel(const T *__restrict__ wide, const T *__restrict__ dout,
+                                       T *__restrict__ dwide, int64_t vectors, int hidden8) {
+    for (int64_t i = blockIdx.x * int64_t(blockDim.x) + threadIdx.x; i < vectors;
+         i += int64_t(gridDim.x) * blockDim.x) {
+        int64_t token = i / hidden8;
+        int c = int(i % hidden8) * 8;
+        float g[8], u[8], dy[8], dg[8], du[8];
+        load8(wide + token * hidden8 * 16 + c, g);
+        load8(wide + token * hidden8 * 16 + hidden8 * 8 + c, u);
+        load8(dout + token * hidden8 * 8 + c, dy);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            float sig = sigmoid(g[j]);
+            float activated = rounded<T>(g[j] * sig);
+            float da = rounded<T>(dy[j] * u[j]);
+            dg[j] = da * sig * (1.f + g[j] * (1.f - sig));
+            du[j] = dy[j] * activated;
+        }
+        store8(dwide + token * hidden8 * 16 + c, dg);
+        store8(dwide + token * hidden8 * 16 + hidden8 * 8 + c, du);
+    }
+}
+void launch_swiglu_backward(Dtype t, const void *wide, const void *dout, void *dwide, int tokens, int hidden,
+                            cudaStream_t s) {
+    int64_t vectors = int64_t(tokens) * (hidden / 8);
+    DISPATCH(t, (swiglu_backward_kernel<T><<<blocks_for(vectors, 256, 148 * 16), 256, 0, s>>>(
+                    (const T *)wide, (const T *)dout, (T *)dwide, vectors, hidden / 8)));
+}
+template <class T> __global__ void gelu_kernel(const T *__restrict__ in, T *__restrict__ out, int64_t vectors) {
+    for (int64_t i = blockIdx.x * int64_t(blockDim.x) + threadIdx.x; i < vectors;
+         i += int64_t(gridDim.x) * blockDim.x) {
+        float v[8];
+        load8(in + i * 8, v);
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+            v[j] = gelu(v[j]);
+        store8(out + i * 8, v);
+    }
+}
+void launch_gelu(Dtype t, const void *in, void *out, int64_t count, cudaStream_t s) {
+    DISPATCH(t, (gelu_kernel<T><<<blocks_for(count / 8, 256, 148 * 16), 256, 0, s>>>((const T *)in, (T *)out,
+                                                                                 count / 8)));
+}
+template <class T>
+__global__ void gelu_backward_kernel(const T *__restrict__ pre, const T *__restrict__ dy, T *__restrict__ dx,
+                                     int64_t vectors) {
+    for (int64_t i = blockIdx.x * int64_t(blockDim.x) + threadIdx.x; i < vectors;
+         i += int64_t(gridDim.x) * blockDim.x) {
+        float v[8], g[8];
+        load8(pre + i * 8, v);
+        load8(dy + i * 8, g);
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+            g[j] *= gelu_derivative(v[j]);
+        store8(dx + i * 8, g);
+    }
+}
+void launch_gelu_backward(Dtype t, const void *pre, const void *dy, void *dx, int64_t count, cudaStream_t s) {
+    DISPATCH(t, (gelu_backward_kernel<T><<<blocks_for(count / 8, 256, 148 * 16), 256, 0, s>>>(
+                    (const T *)pre, (const T *)dy, (T *)dx, count / 8)));
+}
+
+// ------------------------------------------------------------------------------------------
+// 256-way softmax cross-entropy, one warp per row, 8 logits per lane (one 128-bit load):
+// loss = max + log(sum exp) - logit[y]; dlogit = round((softmax - onehot) / divisor).
+// ------------------------------------------------------------------------------------------
+template <class T> __global__ void __launch_bounds__(256) cross_entropy_kernel(CrossEntropyArgs a) {
+    const int lane = threadIdx.x % 32;
+    const int row = blockIdx.x * (blockDim.x / 32) + threadIdx.x / 32;
+    if (row >= a.rows)
+        return;
+    float v[8];
+    load8((const T *)a.logits + int64_t(row) * Vocabulary + lane * 8, v);
+    float high = v[0];
+#pragma unroll
+    for (int j = 1; j < 8; ++j)
+        high = fmaxf(high, v[j]);
+    high = warp_max(high);
+    float e[8], sum = 0;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        e[j] = expf(v[j] - high);
+        sum += e[j];
+    }
+    sum = warp_sum(sum);
+    const int target = a.targets[row];
+    float picked;
+    { // select the target's logit without dynamic register indexing
+        float chosen = v[0];
+#pragma unroll
+        for (int j = 1; j < 8; ++j)
+            chosen = (target % 8 == j) ? v[j] : chosen;
+        picked = __shfl_sync(0xffffffffu, chosen, target / 8);
+    }
+    if (lane == 0)
+        a.losses[row] = high + logf(sum) - picked;
+    if (a.logits_fp32)
+        store8(a.logits_fp32 + int64_t(row) * Vocabulary + lane * 8, v);
+    if (a.dlogits) {
+        float g[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+            g[j] = (e[j] / sum - (lane * 8 + j == target ? 1.f : 0.f)) / a.divisor;
+        store8((T *)a.dlogits + int64_t(row) * Vocabulary + lane * 8, g);
+    }
+}
+void launch_cross_entropy(Dtype t, const CrossEntropyArgs &a, cudaStream_t s) {
+    DISPATCH(t, (cross_entropy_kernel<T><<<blocks_for(a.rows, 8), 256, 0, s>>>(a)));
+}
+
+// Mean over the batch for every position, summed in double like the reference
+// (cuda/trainer.cuh:94-98); row `iteration` of the history.
+__global__ void loss_history_kernel(const float *token_losses, float *history, const StepCounters *counters,
+                                    int batch, int context) {
+    int p = blockIdx.x * blockDim.x + threadIdx.x;
+    if (p >= context)
+        return;
+    double total = 0;
+    for (int b = 0; b < batch; ++b)
+        total += token_losses[int64_t(b) * context + p];
+    history[int64_t(counters->iteration) * context + p] = float(total / batch);
+}
+void launch_loss_history(const float *token_losses, float *history, const StepCounters *counters, int batch,
+                         int context, cudaStream_t s) {
+    loss_history_kernel<<<blocks_for(context, 64), 64, 0, s>>>(token_losses, history, counters, batch, context);
+}
+
+// ------------------------------------------------------------------------------------------
+// Conversions.
+// ------------------------------------------------------------------------------------------
+__global__ void split_weights_kernel(const float *w, bf16 *high, uint16_t *low, int64_t count) {
+    for (int64_t i = blockIdx.x * int64_t(blockDim.x) + threadIdx.x; i < count;
+         i += int64_t(gridDim.x) * blockDim.x) {
+        unsigned bits = __float_as_uint(w[i]);
+        high[i] = __ushort_as_bfloat16((unsigned short)(bits >> 16));
+        low[i] = uint16_t(bits);
+    }
+}
+void launch_split_weights(const float *w, bf16 *high, uint16_t *low, int64_t count, cudaStream_t s) {
+    split_weights_kernel<<<blocks_for(count, 256, 148 * 8), 256, 0, s>>>(w, high, low, count);
+}
+__global__ void join_weights_kernel(const bf16 *high, const uint16_t *low, float *w, int64_t count) {
+    for (int64_t i = blockIdx.x * int64_t(blockDim.x) + threadIdx.x; i < count;
+         i += int64_t(gridDim.x) * blockDim.x)
+        w[i] = join_weight(high[i], low[i]);
+}
+void launch_join_weights(const bf16 *high, const uint16_t *low, float *w, int64_t count, cudaStream_t s) {
+    join_weights_kernel<<<blocks_for(count, 256, 148 * 8), 256, 0, s>>>(high, low, w, count);
+}
+template <class A, class B> __global__ void cast_kernel(const A *in, B *out, int64_t count) {
+    for (int64_t i = blockIdx.x * int64_t(blockDim.x) + threadIdx.x; i < count;
+         i += int64_t(gridDim.x) * blockDim.x)
+        out[i] = from_float<B>(to_float(in[i]));
+}
+void launch_cast(Dtype from, const void *in, Dtype to, void *out, int64_t count, cudaStream_t s) {
+    int blocks = blocks_for(count, 256, 148 * 8);
+    if (from == Dtype::FP32 && to == Dtype::BF16)
+        cast_kernel<<<blocks, 256, 0, s>>>((const float *)in, (bf16 *)out, count);
+    else if (from == Dtype::BF16 && to == Dtype::FP32)
+        cast_kernel<<<blocks, 256, 0, s>>>((const bf16 *)in, (float *)out, count);
+    else
+        CHECK_CUDA(cudaMemcpyAsync(out, in, count * dtype_size(from), cudaMemcpyDeviceToDevice, s));
+}

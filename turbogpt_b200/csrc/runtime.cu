@@ -1,0 +1,290 @@
+// The C ABI: the reference's 22 engine functions (runtime.h:12-37, implemented there by
+// cuda/runtime.cu and cuda/engine_state.cu) plus the extensions declared in
+// include/turbogpt_b200.h.  Every function converts exceptions to the error convention:
+// negative int / NULL and a thread-local message.
+#include "engine.h"
+#include <cstring>
+
+static thread_local std::string last_error;
+
+template <class F> static int guarded(F &&body) {
+    try {
+        body();
+        return 0;
+    } catch (const std::exception &error) {
+        last_error = error.what();
+        return -1;
+    }
+}
+
+extern "C" {
+
+const char *tg_error(void) { return last_error.c_str(); }
+
+void tg_ex_reference_config(const TgConfig *base, TgConfigEx *c) {
+    memset(c, 0, sizeof(*c));
+    c->base = *base;
+    c->struct_size = sizeof(TgConfigEx);
+    c->width = 16, c->heads = 4, c->hidden = 48;
+    c->norm = TG_NORM_RMS, c->attention = TG_ATTENTION_ARGMAX, c->mlp = TG_MLP_SWIGLU, c->tied = 0;
+    c->rope = TG_ROPE_PARTIAL, c->hidden_optimizer = TG_HIDDEN_MUON, c->precision = TG_PRECISION_BF16;
+    c->world = 1, c->rank = 0;
+}
+void tg_ex_gpt_config(const TgConfig *base, int width, int heads, int hidden, TgConfigEx *c) {
+    tg_ex_reference_config(base, c);
+    c->width = width, c->heads = heads, c->hidden = hidden;
+    c->norm = TG_NORM_LAYER, c->attention = TG_ATTENTION_SOFTMAX, c->mlp = TG_MLP_GELU, c->tied = 1;
+    c->rope = TG_ROPE_NONE, c->hidden_optimizer = TG_HIDDEN_ADAMW;
+}
+
+Engine *tg_create_ex(const TgConfigEx *config) {
+    try {
+        if (!config)
+            throw std::runtime_error("Missing configuration");
+        return new Engine(*config);
+    } catch (const std::exception &error) {
+        last_error = error.what();
+        return nullptr;
+    }
+}
+Engine *tg_create(const TgConfig *config) {
+    try {
+        if (!config)
+            throw std::runtime_error("Missing configuration");
+        // The reference's own limits (cuda/runtime.cu:65-68), minus the tile-balance rule of its
+        // persistent kernel: any depth up to 64 and any context are accepted here.
+        if (config->batch < 4 || int64_t(config->batch) * config->context % 16)
+            throw std::runtime_error("Supported: batch at least 4 with batch*context divisible by 16");
+        TgConfigEx ex;
+        tg_ex_reference_config(config, &ex);
+        return new Engine(ex);
+    } catch (const std::exception &error) {
+        last_error = error.what();
+        return nullptr;
+    }
+}
+void tg_destroy(Engine *engine) { delete engine; }
+int tg_parameter_count(Engine *e) { return int(e->layout.count); }
+int tg_blocks(Engine *e) { return e->sms; }
+int tg_shared_bytes(Engine *e) { return e->tensor_cores ? gemm_tc_shared_bytes() : 0; }
+
+int tg_set_weights(Engine *e, const float *w) {
+    return guarded([&] {
+        if (!w)
+            throw std::runtime_error("Missing weights");
+        e->set_weights(w);
+    });
+}
+int tg_get_weights(Engine *e, float *w) {
+    return guarded([&] {
+        if (!w)
+            throw std::runtime_error("Missing weights output");
+        e->get_weights(w);
+    });
+}
+int tg_get_optimizer_state(Engine *e, float *m, float *v, uint64_t *step) {
+    return guarded([&] { e->get_optimizer_state(m, v, step); });
+}
+int tg_set_optimizer_state(Engine *e, const float *m, const float *v, uint64_t step) {
+    return guarded([&] { e->set_optimizer_state(m, v, step); });
+}
+int tg_memory(Engine *e, double *used_gb) {
+    return guarded([&] {
+        if (!used_gb)
+            throw std::runtime_error("Missing memory output");
+        *used_gb = double(e->allocated_bytes) / (1024.0 * 1024.0 * 1024.0);
+    });
+}
+int tg_set_data(Engine *e, const uint8_t *bytes, int64_t size) {
+    return guarded([&] {
+        if (!bytes)
+            throw std::runtime_error("Missing dataset");
+        e->set_data(bytes, size);
+    });
+}
+int tg_train(Engine *e, int steps) {
+    return guarded([&] { e->train(steps); });
+}
+int tg_get_training_losses(Engine *e, float *per_position, int count) {
+    return guarded([&] { e->training_losses(per_position, count); });
+}
+int tg_training_versions(Engine *e, int *versions, int count) {
+    return guarded([&] { // synchronous training: every step sees the weights of the step before it
+        if (count < 0 || count > e->last_train_steps)
+            throw std::runtime_error("Version trace exceeds last training launch");
+        for (int i = 0; i < count; ++i)
+            versions[i] = int(e->step) - e->last_train_steps + i;
+    });
+}
+int tg_pipeline_stats(Engine *, double *mean_staleness, int *max_staleness) {
+    return guarded([&] {
+        *mean_staleness = 0;
+        *max_staleness = 0;
+    });
+}
+int tg_onecycle_point(const TgOneCycle *schedule, int step, TgStepRates *rates) {
+    return guarded([&] { *rates = onecycle_point(*schedule, step); });
+}
+int tg_set_onecycle(Engine *e, const TgOneCycle *schedule) {
+    return guarded([&] { e->set_onecycle(*schedule); });
+}
+int tg_batch(Engine *e, const uint8_t *x, const uint8_t *y, float *logits, float *gradients, float *per_position) {
+    return guarded([&] {
+        if (!x || !y)
+            throw std::runtime_error("Missing batch input");
+        e->batch(x, y, logits, gradients, per_position);
+    });
+}
+int tg_predict(Engine *e, const uint8_t *context, float *logits) {
+    return guarded([&] { e->predict(context, logits); });
+}
+int tg_optimizer_test(Engine *e, const float *gradients, int steps) {
+    return guarded([&] {
+        if (!gradients)
+            throw std::runtime_error("Missing gradients");
+        e->optimizer_test(gradients, steps);
+    });
+}
+int tg_synchronize(Engine *e) {
+    return guarded([&] {
+        e->set_device();
+        CHECK_CUDA(cudaStreamSynchronize(e->stream));
+    });
+}
+
+// ---------------------------------------------------------------------------- extensions -----
+int64_t tg_ex_parameter_count(const TgConfigEx *config) {
+    try {
+        validate_config(*config);
+        return make_layout(*config).count;
+    } catch (const std::exception &error) {
+        last_error = error.what();
+        return -1;
+    }
+}
+int tg_ex_parameter_layout(const TgConfigEx *config, int64_t *offsets, int32_t *rows, int32_t *cols, int capacity) {
+    try {
+        validate_config(*config);
+        Layout p = make_layout(*config);
+        int n = int(p.tensors.size());
+        for (int i = 0; i < n && i < capacity; ++i) {
+            offsets[i] = p.tensors[i].offset;
+            rows[i] = p.tensors[i].rows;
+            cols[i] = p.tensors[i].cols;
+        }
+        return n;
+    } catch (const std::exception &error) {
+        last_error = error.what();
+        return -1;
+    }
+}
+int tg_ex_initialize_weights(const TgConfigEx *config, float *weights) {
+    return guarded([&] {
+        validate_config(*config);
+        initialize_weights(*config, weights);
+    });
+}
+int tg_ex_nccl_unique_id(uint8_t *id128) {
+    return guarded([&] {
+        const Nccl &nccl = Nccl::get();
+        Nccl::UniqueId id;
+        nccl.check(nccl.GetUniqueId(&id), "ncclGetUniqueId");
+        memcpy(id128, id.internal, 128);
+    });
+}
+void *tg_ex_stream(Engine *e) { return e->stream; }
+int tg_ex_sample(Engine *e, uint64_t step, uint8_t *x, uint8_t *y) {
+    return guarded([&] { e->sample(step, x, y); });
+}
+int tg_ex_train_mean_loss(Engine *e, int steps, float *mean_loss) {
+    return guarded([&] { *mean_loss = e->train_mean_loss(steps); });
+}
+int tg_ex_profile(Engine *e, const char **names, double *milliseconds, int64_t *launches, int capacity, int reset) {
+    try {
+        e->set_device();
+        e->flush_profile();
+        for (int i = 0; i < FamilyCount && i < capacity; ++i) {
+            names[i] = family_names[i];
+            milliseconds[i] = e->family_ms[i];
+            launches[i] = e->family_launches[i];
+        }
+        if (reset)
+            for (int i = 0; i < FamilyCount; ++i)
+                e->family_ms[i] = 0, e->family_launches[i] = 0;
+        return FamilyCount;
+    } catch (const std::exception &error) {
+        last_error = error.what();
+        return -1;
+    }
+}
+int64_t tg_ex_launch_count(Engine *e) { return e->launches; }
+
+static int device_sms() {
+    int device = 0, sms = 0;
+    CHECK_CUDA(cudaGetDevice(&device));
+    CHECK_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
+    return sms;
+}
+static void require_sm100() {
+    int device = 0, major = 0;
+    CHECK_CUDA(cudaGetDevice(&device));
+    CHECK_CUDA(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device));
+    if (major != 10)
+        throw std::runtime_error("This library is built for sm_100a (B200)");
+}
+
+int tg_ex_gemm(const void *a, int64_t a_row, int64_t a_col, const void *b, int64_t b_row, int64_t b_col, void *c,
+               int64_t ldc, int m, int n, int k, int out_fp32, int tensor_cores, void *stream) {
+    return guarded([&] {
+        require_sm100();
+        GemmArgs g;
+        g.a = a, g.a_row = a_row, g.a_col = a_col, g.b = b, g.b_row = b_row, g.b_col = b_col;
+        g.c = c, g.ldc = ldc, g.m = m, g.n = n, g.k = k;
+        g.in = Dtype::BF16, g.out = out_fp32 ? Dtype::FP32 : Dtype::BF16;
+        if (tensor_cores) {
+            if (!gemm_tc_supported(g))
+                throw std::runtime_error("GEMM shape or layout is outside the tensor-core kernel's range");
+            launch_gemm_tc(g, device_sms(), nullptr, static_cast<cudaStream_t>(stream));
+        } else {
+            launch_gemm_simt(g, static_cast<cudaStream_t>(stream));
+        }
+        CHECK_CUDA(cudaGetLastError());
+    });
+}
+int tg_ex_attention_forward(const void *qkv, void *out, float *lse, int batch, int context, int heads, int d_head,
+                            int tensor_cores, void *stream) {
+    return guarded([&] {
+        require_sm100();
+        if (tensor_cores)
+            throw std::runtime_error("tensor-core attention is not available in this build");
+        SoftmaxAttentionArgs a{qkv, out, lse, batch, context, heads * d_head, heads};
+        launch_softmax_attention(Dtype::BF16, a, static_cast<cudaStream_t>(stream));
+        CHECK_CUDA(cudaGetLastError());
+    });
+}
+int tg_ex_attention_backward(const void *qkv, const void *out, const void *dout, const float *lse, void *dqkv,
+                             int batch, int context, int heads, int d_head, int tensor_cores, void *stream) {
+    return guarded([&] {
+        require_sm100();
+        if (tensor_cores)
+            throw std::runtime_error("tensor-core attention is not available in this build");
+        float *delta = nullptr;
+        CHECK_CUDA(cudaMallocAsync(&delta, size_t(batch) * heads * context * sizeof(float),
+                                   static_cast<cudaStream_t>(stream)));
+        SoftmaxAttentionBackwardArgs a{qkv, out, dout, lse, delta, dqkv, batch, context, heads * d_head, heads};
+        launch_softmax_attention_backward(Dtype::BF16, a, static_cast<cudaStream_t>(stream));
+        CHECK_CUDA(cudaFreeAsync(delta, static_cast<cudaStream_t>(stream)));
+        CHECK_CUDA(cudaGetLastError());
+    });
+}
+int tg_ex_cross_entropy(const void *logits, const uint8_t *targets, float *losses, void *dlogits, int rows,
+                        float scale, void *stream) {
+    return guarded([&] {
+        require_sm100();
+        CrossEntropyArgs a{logits, targets, losses, dlogits, nullptr, 1.f / scale, rows};
+        launch_cross_entropy(Dtype::BF16, a, static_cast<cudaStream_t>(stream));
+        CHECK_CUDA(cudaGetLastError());
+    });
+}
+
+} // extern "C"

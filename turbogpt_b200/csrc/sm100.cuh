@@ -1,0 +1,201 @@
+// sm_100a primitives in inline PTX: mbarrier, TMA tile loads, tcgen05 (TMEM allocation, MMA,
+// commit, TMEM loads), shared-memory and instruction descriptors, and host-side tensor maps.
+// Every wait is bounded: a wait that gives up records a code in StepCounters::error and makes
+// the kernel drain and return instead of hanging the GPU.
+#pragma once
+#include "common.h"
+#include "kernels.cuh"
+#include <cuda.h>
+
+namespace sm100 {
+
+// ------------------------------------------------------------------ host: tensor maps -------
+// cuTensorMapEncodeTiled is fetched through the runtime so the library has no link-time
+// dependency on libcuda.
+using TensorMapEncoder = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                      const cuuint64_t *, const cuuint32_t *, const cuuint32_t *,
+                                      CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                      CUtensorMapFloatOOBfill);
+inline TensorMapEncoder tensor_map_encoder() {
+    static TensorMapEncoder fn = [] {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult status;
+        CHECK_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &status));
+        if (!p || status != cudaDriverEntryPointSuccess)
+            throw std::runtime_error("cuTensorMapEncodeTiled is not available in this driver");
+        return reinterpret_cast<TensorMapEncoder>(p);
+    }();
+    return fn;
+}
+// BF16 tensor [batch][outer][inner] with `inner` contiguous, `ld` elements between outer rows and
+// `batch_stride` elements between batches; box [1][box_outer][box_inner]; 128-byte swizzle.
+// Out-of-range box parts are filled with zeros.
+inline CUtensorMap make_map_bf16(const void *base, uint64_t inner, uint64_t outer, uint64_t batch, uint64_t ld,
+                                 uint64_t batch_stride, uint32_t box_inner, uint32_t box_outer) {
+    if (reinterpret_cast<uintptr_t>(base) % 16 || ld % 8 || batch_stride % 8 || box_inner * 2 != 128 ||
+        box_outer > 256)
+        throw std::runtime_error("tensor map: operand is not 16-byte aligned or the box is out of range");
+    CUtensorMap map;
+    cuuint64_t dims[3] = {inner, outer, batch};
+    cuuint64_t strides[2] = {ld * 2, (batch > 1 ? batch_stride : ld * outer) * 2};
+    cuuint32_t box[3] = {box_inner, box_outer, 1};
+    cuuint32_t element_strides[3] = {1, 1, 1};
+    CUresult r = tensor_map_encoder()(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void *>(base), dims,
+                                      strides, box, element_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                      CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+        throw std::runtime_error("cuTensorMapEncodeTiled failed with code " + std::to_string(int(r)));
+    return map;
+}
+
+#ifdef __CUDACC__
+// ------------------------------------------------------------------ device ------------------
+__device__ __forceinline__ uint32_t smem_address(const void *p) {
+    return uint32_t(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ bool elect_one() {
+    uint32_t is_elected;
+    asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(is_elected));
+    return is_elected != 0;
+}
+__device__ __forceinline__ unsigned long long global_timer() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+__device__ __forceinline__ void mbarrier_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void fence_barrier_init() {
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void fence_async_proxy() {
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void mbarrier_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbarrier_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbarrier_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+                 "selp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(done)
+                 : "r"(bar), "r"(parity)
+                 : "memory");
+    return done != 0;
+}
+// Waits for the phase with the given parity.  Gives up after ~2 s of wall time or as soon as
+// another role of this CTA has raised `*abort_flag`; then raises the flag, records `code` and
+// returns false.  Callers leave their loops on false.
+constexpr unsigned long long WaitLimitNs = 2000000000ull;
+__device__ __forceinline__ bool mbarrier_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag,
+                                              StepCounters *counters, int code) {
+    if (mbarrier_try_wait(bar, parity))
+        return true;
+    const unsigned long long start = global_timer();
+    for (unsigned spins = 1;; ++spins) {
+        if (mbarrier_try_wait(bar, parity))
+            return true;
+        if ((spins & 0xff) == 0) {
+            if (*abort_flag)
+                return false;
+            if (global_timer() - start > WaitLimitNs) {
+                *abort_flag = 1;
+                if (counters)
+                    atomicCAS(&counters->error, 0, code);
+                return false;
+            }
+        }
+    }
+}
+
+// 3-D tile load (inner, outer, batch coordinates) completing on an mbarrier.
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *map, int x, int y, int z,
+                                            uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes "
+                 "[%0], [%1, {%3, %4, %5}], [%2];" ::"r"(dst),
+                 "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y), "r"(z)
+                 : "memory");
+}
+__device__ __forceinline__ void prefetch_map(const CUtensorMap *map) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
+}
+
+// ---- tensor memory ----
+__device__ __forceinline__ void tmem_alloc(uint32_t result_slot, uint32_t columns) { // whole warp
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(result_slot),
+                 "r"(columns)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t address, uint32_t columns) { // whole warp
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(address), "r"(columns) : "memory");
+}
+__device__ __forceinline__ void tcgen05_fence_before() {
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tcgen05_fence_after() {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+// Arrives on the mbarrier once all MMAs issued so far by this thread have completed.
+__device__ __forceinline__ void tcgen05_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
+                 : "memory");
+}
+// D[tmem] (+)= A[smem] * B[smem]; BF16 operands, FP32 accumulator.
+__device__ __forceinline__ void tcgen05_mma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                                 uint32_t instruction, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+                 "l"(a_desc), "l"(b_desc), "r"(instruction), "r"(accumulate)
+                 : "memory");
+}
+// 32 lanes x 32 consecutive FP32 columns: thread i of the warp receives row (lane base + i).
+__device__ __forceinline__ void tmem_load_32x32(uint32_t address, float (&v)[32]) {
+    uint32_t r[32];
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                 "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]),
+                   "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]),
+                   "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]),
+                   "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                 : "r"(address)
+                 : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 32; ++i)
+        v[i] = __uint_as_float(r[i]);
+}
+
+// ---- descriptors ----
+// Shared-memory matrix descriptor for 128-byte-swizzled BF16 tiles (version 1 = Blackwell).
+//   K-major  (rows of 64 K-elements = 128 B, 8-row atoms of 1024 B): SBO = 1024 B between atoms.
+//   MN-major (rows of 64 MN-elements = 128 B per K index, 8-K atoms of 1024 B): SBO = 1024 B
+//   between 8-K atoms, LBO = bytes between consecutive 64-element MN blocks.
+__device__ __forceinline__ uint64_t smem_descriptor(uint32_t address, uint32_t leading_bytes, uint32_t stride_bytes) {
+    uint64_t d = 0;
+    d |= uint64_t((address & 0x3ffff) >> 4);
+    d |= uint64_t((leading_bytes >> 4) & 0x3fff) << 16;
+    d |= uint64_t((stride_bytes >> 4) & 0x3fff) << 32;
+    d |= uint64_t(1) << 46; // descriptor version
+    d |= uint64_t(2) << 61; // 128-byte swizzle
+    return d;
+}
+// Instruction descriptor: BF16 x BF16 -> FP32, M x N tile, operand majorness (0 = K, 1 = MN).
+__host__ __device__ inline uint32_t instruction_descriptor(int m, int n, int a_mn_major, int b_mn_major) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | (uint32_t(a_mn_major) << 15) | (uint32_t(b_mn_major) << 16) |
+           (uint32_t(n >> 3) << 17) | (uint32_t(m >> 4) << 24);
+}
+#endif // __CUDACC__
+
+} // namespace sm100
