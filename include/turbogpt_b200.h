@@ -127,6 +127,10 @@ int tg_ex_sample(Engine *engine, uint64_t step, uint8_t *x, uint8_t *y);
 /* Device-resident variant of tg_train + tg_get_training_losses for benchmarks: runs `steps`
  * steps and returns the mean loss of the last one. */
 int tg_ex_train_mean_loss(Engine *engine, int steps, float *mean_loss);
+/* One optimizer step on caller-supplied host bytes x, y [batch*context] (instead of sampling the
+ * resident corpus); writes the per-position mean loss [context] when per_position != NULL, which
+ * synchronises.  The host-buffer counterpart of tg_train for callers that stream their own batches. */
+int tg_ex_train_batch(Engine *engine, const uint8_t *x, const uint8_t *y, float *per_position);
 /* Per-kernel-family device time accumulated since the last reset (TG_FLAG_PROFILE engines).
  * names: up to `capacity` pointers to static strings; returns the number of families. */
 int tg_ex_profile(Engine *engine, const char **names, double *milliseconds, int64_t *launches,

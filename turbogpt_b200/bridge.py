@@ -128,6 +128,7 @@ def load_library() -> C.CDLL:
     lib.tg_ex_stream.restype = P
     lib.tg_ex_sample.argtypes = [P, C.c_uint64, P, P]
     lib.tg_ex_train_mean_loss.argtypes = [P, I, C.POINTER(C.c_float)]
+    lib.tg_ex_train_batch.argtypes = [P, P, P, P]
     lib.tg_ex_profile.argtypes = [P, P, P, P, I, I]
     lib.tg_ex_launch_count.argtypes = [P]
     lib.tg_ex_launch_count.restype = I64
@@ -143,7 +144,7 @@ EXPORTS = ('error create destroy parameter_count blocks shared_bytes set_weights
            'set_optimizer_state memory set_data train get_training_losses training_versions pipeline_stats '
            'onecycle_point set_onecycle batch predict optimizer_test synchronize').split()
 EXTENSIONS = ('reference_config gpt_config parameter_count parameter_layout initialize_weights nccl_unique_id '
-              'stream sample train_mean_loss profile launch_count gemm attention_forward attention_backward '
+              'stream sample train_mean_loss train_batch profile launch_count gemm attention_forward attention_backward '
               'cross_entropy').split()
 
 
@@ -213,6 +214,13 @@ class Native:
     def training_losses(self, count):
         out = np.empty((count, self.config.context), np.float32)
         self.check(self.lib.tg_get_training_losses(self.handle, out.ctypes.data, count))
+        return out
+
+    def train_batch(self, x, y, want_losses=True):
+        x, y = np.ascontiguousarray(x, dtype=np.uint8), np.ascontiguousarray(y, dtype=np.uint8)
+        out = np.empty(self.config.context, np.float32) if want_losses else None
+        self.check(self.lib.tg_ex_train_batch(self.handle, x.ctypes.data, y.ctypes.data,
+                                              out.ctypes.data if want_losses else None))
         return out
 
     def optimizer_test(self, gradient, steps=1):

@@ -731,3 +731,26 @@ void Engine::get_optimizer_state(float *m, float *v, uint64_t *at_step) {
     CHECK_CUDA(cudaStreamSynchronize(stream));
     *at_step = step;
 }
+
+// One optimizer step on bytes supplied by the caller instead of the resident corpus.
+void Engine::train_batch(const uint8_t *bx, const uint8_t *by, float *per_position) {
+    set_device();
+    if (!bx || !by)
+        throw std::runtime_error("Missing batch input");
+    if (schedule && step + 1 > uint64_t(schedule_steps))
+        throw std::runtime_error("Training would exceed the OneCycle schedule");
+    CHECK_CUDA(cudaMemcpyAsync(x, bx, tokens, cudaMemcpyHostToDevice, stream));
+    CHECK_CUDA(cudaMemcpyAsync(y, by, tokens, cudaMemcpyHostToDevice, stream));
+    CHECK_CUDA(cudaMemsetAsync(&counters->iteration, 0, sizeof(int), stream));
+    forward(true, false);
+    run(FMisc, [&] {
+        launch_loss_history(token_losses, loss_history, counters, config.base.batch, config.base.context, stream);
+    });
+    backward();
+    optimize();
+    step += 1;
+    last_train_steps = 1;
+    losses_reduced = false;
+    if (per_position)
+        training_losses(per_position, 1);
+}

@@ -111,6 +111,7 @@ struct Engine {
     void set_optimizer_state(const float *m, const float *v, uint64_t at_step);
     void get_optimizer_state(float *m, float *v, uint64_t *at_step);
     float train_mean_loss(int steps);
+    void train_batch(const uint8_t *bx, const uint8_t *by, float *per_position);
     void flush_profile();
 
   private:

@@ -199,6 +199,9 @@ int tg_ex_sample(Engine *e, uint64_t step, uint8_t *x, uint8_t *y) {
 int tg_ex_train_mean_loss(Engine *e, int steps, float *mean_loss) {
     return guarded([&] { *mean_loss = e->train_mean_loss(steps); });
 }
+int tg_ex_train_batch(Engine *e, const uint8_t *x, const uint8_t *y, float *per_position) {
+    return guarded([&] { e->train_batch(x, y, per_position); });
+}
 int tg_ex_profile(Engine *e, const char **names, double *milliseconds, int64_t *launches, int capacity, int reset) {
     try {
         e->set_device();
