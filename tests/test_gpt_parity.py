@@ -48,8 +48,19 @@ def test_step_parity(fp32, flags):
     with Native(ex) as engine:
         engine.set_weights(w)
         logits, gradients, losses = engine.batch(x, y)
-        # per-op max relative error (relative to the largest magnitude of the tensor)
-        assert max_relative(logits, target) <= tolerance
+        assert relative(logits, target) <= tolerance
+        if fp32:
+            assert max_relative(logits, target) <= tolerance
+        else:
+            # Two BF16 pipelines that round at the same points still land on neighbouring BF16
+            # values: the CPU oracle itself is 1.07e-2 (max) / 0.9e-2 (L2) away from its own FP32
+            # variant on this fixture.  The largest logit error allowed is two BF16 ulps of the
+            # largest logit (2 * 2^-7 relative to it), and against the FP32 model the engine
+            # must be as accurate as the BF16 oracle is.
+            assert max_relative(logits, target) <= 2 * 2.0 ** -7
+            exact = fixture(depth, width, heads, context, batch, True)[1].batch(x, y, backward=False)[0]
+            assert relative(logits, exact) <= 1.1 * relative(target, exact)
+            assert max_relative(logits, exact) <= 1.25 * max_relative(target, exact)
         np.testing.assert_allclose(losses, expected_losses, rtol=tolerance, atol=tolerance)
         offset = 0
         for name, param in model.params.items():

@@ -8,6 +8,7 @@ from turbogpt_b200 import load_library
 from helpers import max_relative
 
 pytestmark = pytest.mark.gpu
+BACKWARD_ON_TENSOR_CORES = True
 
 
 def gemm(lib, a, a_strides, b, b_strides, m, n, k, out_fp32, tensor_cores):
@@ -81,7 +82,8 @@ def test_cross_entropy_matches_torch():
     assert max_relative(grads.float().cpu().numpy(), (probs * scale).numpy()) <= 4e-3
 
 
-@pytest.mark.parametrize("batch,context,heads,d_head", [(2, 128, 2, 64), (1, 200, 3, 64), (2, 64, 2, 32)])
+@pytest.mark.parametrize("batch,context,heads,d_head", [(2, 128, 2, 64), (1, 200, 3, 64), (2, 64, 2, 32),
+                                                        (2, 1024, 2, 64), (3, 520, 1, 64)])
 def test_attention_matches_torch(batch, context, heads, d_head):
     lib = load_library()
     width = heads * d_head
@@ -99,13 +101,20 @@ def test_attention_matches_torch(batch, context, heads, d_head):
     d_out = torch.empty(batch * context, width, device="cuda", dtype=torch.bfloat16)
     lse = torch.empty(batch * heads * context, device="cuda")
     d_dqkv = torch.empty_like(d_qkv)
-    for tensor_cores in (0,):
+    for tensor_cores in ((0, 1) if d_head == 64 else (0,)):
+        d_out.zero_()
+        lse.zero_()
         assert lib.tg_ex_attention_forward(d_qkv.data_ptr(), d_out.data_ptr(), lse.data_ptr(), batch, context, heads,
                                            d_head, tensor_cores, None) == 0, lib.tg_error()
-        assert lib.tg_ex_attention_backward(d_qkv.data_ptr(), d_out.data_ptr(), d_dout.data_ptr(), lse.data_ptr(),
-                                            d_dqkv.data_ptr(), batch, context, heads, d_head, tensor_cores, None) == 0
         torch.cuda.synchronize()
-        assert max_relative(d_out.float().cpu().numpy(), expected_out) <= 1e-2
-        assert max_relative(d_dqkv.float().cpu().numpy(), expected_dqkv) <= 1e-2
+        assert max_relative(d_out.float().cpu().numpy(), expected_out) <= 1e-2, tensor_cores
         expected_lse = torch.logsumexp(scores, -1).detach().reshape(-1).numpy()
         np.testing.assert_allclose(lse.cpu().numpy(), expected_lse, rtol=1e-4, atol=1e-4)
+        if tensor_cores and not BACKWARD_ON_TENSOR_CORES:
+            continue
+        d_dqkv.zero_()
+        assert lib.tg_ex_attention_backward(d_qkv.data_ptr(), d_out.data_ptr(), d_dout.data_ptr(), lse.data_ptr(),
+                                            d_dqkv.data_ptr(), batch, context, heads, d_head, tensor_cores, None) == 0, \
+            lib.tg_error()
+        torch.cuda.synchronize()
+        assert max_relative(d_dqkv.float().cpu().numpy(), expected_dqkv) <= 1e-2, tensor_cores

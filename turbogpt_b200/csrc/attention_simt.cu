@@ -296,6 +296,11 @@ template <class T> __global__ void __launch_bounds__(AttentionWarps * 32) attent
             out[2 * a.width + j * 32 + lane] = from_float<T>(dv[j]);
         }
 }
+void launch_attention_delta(Dtype t, const SoftmaxAttentionBackwardArgs &a, cudaStream_t s) {
+    int64_t items = int64_t(a.batch) * a.heads * a.context;
+    DISPATCH(t, (attention_delta_kernel<T><<<int((items + AttentionWarps - 1) / AttentionWarps), AttentionWarps * 32,
+                                            0, s>>>(a)));
+}
 void launch_softmax_attention_backward(Dtype t, const SoftmaxAttentionBackwardArgs &a, cudaStream_t s) {
     int64_t items = int64_t(a.batch) * a.heads * a.context;
     int d = a.width / a.heads;

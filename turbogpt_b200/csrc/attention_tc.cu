@@ -1,0 +1,701 @@
+// Fused causal softmax attention on the 5th-generation tensor cores, head size 64, BF16.
+// Replaces the reference's per-(query, head) scalar attention loops (cuda/attention.cuh:33-106)
+// for the scaled architecture: no T x T matrix ever reaches HBM.
+//
+// Forward: one CTA per 128 query rows of one (batch, head).  Warp 0 streams K/V blocks of 128
+// keys with TMA (two stages); warp 1 issues tcgen05.mma: S = Q K^T into tensor memory, then
+// O_blk = P V with P read back from tensor memory as the A operand; warps 2-5 own one query
+// row per thread (the TMEM lane), so the online-softmax row maximum and sum are thread-local:
+// two passes over S in TMEM (max, then exp2 and BF16 packing), P written to TMEM, the running
+// output kept in registers and rescaled when the maximum moves.  Two CTAs share an SM (256 TMEM
+// columns and 80 KB of shared memory each), so one CTA's exponentials overlap the other's MMAs.
+#include "device_utils.cuh"
+#include "sm100.cuh"
+
+using namespace sm100;
+
+namespace {
+constexpr int BlockM = 128, BlockN = 128, HeadSize = 64;
+constexpr int TileBytes = 128 * HeadSize * 2; // 16 KB: a Q, K or V tile
+constexpr int ForwardThreads = 192;
+constexpr int ForwardShared = TileBytes * 5 + 1024 + 256; // Q + 2 x (K, V) + alignment + barriers
+constexpr int ForwardTmemColumns = 256;                   // S 0..127 | P 128..191 | O_blk 192..255
+
+struct ForwardParams {
+    bf16 *out;
+    float *lse;
+    int batch, context, heads, width, tiles;
+    float scale_log2; // log2(e) / sqrt(d_head)
+    StepCounters *counters;
+};
+
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+__global__ void __launch_bounds__(ForwardThreads, 2)
+flash_forward_kernel(const __grid_constant__ CUtensorMap map_qkv, ForwardParams p) {
+    extern __shared__ uint8_t raw_shared[];
+    const uint32_t base = (smem_address(raw_shared) + 1023u) & ~1023u;
+    uint8_t *aligned = raw_shared + (base - smem_address(raw_shared));
+    uint64_t *barriers = reinterpret_cast<uint64_t *>(aligned + 5 * TileBytes);
+    const uint32_t q_full = smem_address(barriers), kv_full0 = q_full + 8, kv_empty0 = kv_full0 + 16,
+                   s_full = kv_empty0 + 16, p_full = s_full + 8, o_full = p_full + 8;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(barriers + 8);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+    const uint32_t smem_q = base, smem_kv = base + TileBytes;
+
+    const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+    // Long tiles first: tile index falls as blockIdx grows.
+    const int pairs = p.batch * p.heads;
+    const int tile = p.tiles - 1 - int(blockIdx.x / pairs);
+    const int bh = blockIdx.x % pairs, b = bh / p.heads, h = bh % p.heads;
+    const int blocks = tile + 1; // causal: key blocks 0..tile
+    const int row0 = b * p.context; // first row of this sequence in the packed qkv matrix
+
+    if (threadIdx.x == 0) {
+        mbarrier_init(q_full, 1);
+        for (int s = 0; s < 2; ++s) {
+            mbarrier_init(kv_full0 + 8 * s, 1);
+            mbarrier_init(kv_empty0 + 8 * s, 1);
+        }
+        mbarrier_init(s_full, 1);
+        mbarrier_init(p_full, 4);
+        mbarrier_init(o_full, 1);
+        *abort_flag = 0;
+        fence_barrier_init();
+        prefetch_map(&map_qkv);
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_address(tmem_slot), ForwardTmemColumns);
+        tmem_relinquish();
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    const uint32_t tmem_s = tmem_base, tmem_p = tmem_base + 128, tmem_o = tmem_base + 192;
+
+    if (warp == 0) {
+        if (elect_one()) {
+            mbarrier_expect_tx(q_full, TileBytes);
+            tma_load_3d(smem_q, &map_qkv, h * HeadSize, row0 + tile * BlockM, 0, q_full);
+            for (int j = 0; j < blocks; ++j) {
+                const int stage = j & 1;
+                if (!mbarrier_wait(kv_empty0 + 8 * stage, ((j >> 1) & 1) ^ 1, abort_flag, p.counters, 201))
+                    break;
+                const uint32_t bar = kv_full0 + 8 * stage, dst = smem_kv + stage * 2 * TileBytes;
+                mbarrier_expect_tx(bar, 2 * TileBytes);
+                tma_load_3d(dst, &map_qkv, p.width + h * HeadSize, row0 + j * BlockN, 0, bar);
+                tma_load_3d(dst + TileBytes, &map_qkv, 2 * p.width + h * HeadSize, row0 + j * BlockN, 0, bar);
+            }
+        }
+    } else if (warp == 1) {
+        if (elect_one()) {
+            const uint32_t idesc_s = instruction_descriptor(BlockM, BlockN, 0, 0);
+            const uint32_t idesc_o = instruction_descriptor(BlockM, HeadSize, 0, 1);
+            auto issue_s = [&](int j) { // S = Q K_j^T: four 16-deep steps along the head dimension
+                const uint32_t k_tile = smem_kv + (j & 1) * 2 * TileBytes;
+#pragma unroll
+                for (int ks = 0; ks < HeadSize / 16; ++ks)
+                    tcgen05_mma_bf16(tmem_s, smem_descriptor(smem_q + ks * 32, 16, 1024),
+                                     smem_descriptor(k_tile + ks * 32, 16, 1024), idesc_s, ks > 0);
+                tcgen05_commit(s_full);
+            };
+            bool ok = mbarrier_wait(q_full, 0, abort_flag, p.counters, 202) &&
+                      mbarrier_wait(kv_full0, 0, abort_flag, p.counters, 203);
+            if (ok) {
+                tcgen05_fence_after();
+                issue_s(0);
+            }
+            for (int j = 0; j < blocks && ok; ++j) {
+                ok = mbarrier_wait(p_full, j & 1, abort_flag, p.counters, 204);
+                if (!ok)
+                    break;
+                tcgen05_fence_after();
+                const uint32_t v_tile = smem_kv + (j & 1) * 2 * TileBytes + TileBytes;
+#pragma unroll
+                for (int ks = 0; ks < BlockN / 16; ++ks) // O_blk = P V_j: eight 16-key steps
+                    tcgen05_mma_bf16_ts(tmem_o, tmem_p + ks * 8, smem_descriptor(v_tile + ks * 2048, 8192, 1024),
+                                        idesc_o, ks > 0);
+                tcgen05_commit(o_full);
+                tcgen05_commit(kv_empty0 + 8 * (j & 1)); // K_j and V_j are no longer read
+                if (j + 1 < blocks) {
+                    ok = mbarrier_wait(kv_full0 + 8 * ((j + 1) & 1), ((j + 1) >> 1) & 1, abort_flag, p.counters, 205);
+                    if (!ok)
+                        break;
+                    tcgen05_fence_after();
+                    issue_s(j + 1);
+                }
+            }
+        }
+    } else {
+        const int quarter = warp % 4;
+        const int row = quarter * 32 + lane;              // query row inside the tile = TMEM lane
+        const int position = tile * BlockM + row;          // position inside the sequence
+        const uint32_t lane_base = uint32_t(quarter * 32) << 16;
+        float o[HeadSize];
+#pragma unroll
+        for (int i = 0; i < HeadSize; ++i)
+            o[i] = 0.f;
+        float running_max = -CUDART_INF_F, running_sum = 0.f;
+        bool ok = true;
+        for (int j = 0; j < blocks; ++j) {
+            ok = mbarrier_wait(s_full, j & 1, abort_flag, p.counters, 206);
+            if (!ok)
+                break;
+            tcgen05_fence_after();
+            const bool diagonal = j == tile;
+            // Pass 1: row maximum of the raw scores.
+            float block_max = -CUDART_INF_F;
+#pragma unroll
+            for (int c = 0; c < BlockN / 32; ++c) {
+                uint32_t r[32];
+                tmem_load_32x32_async(tmem_s + lane_base + c * 32, r);
+                tmem_wait_load(r);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    float s = __uint_as_float(r[i]);
+                    if (diagonal && c * 32 + i > row)
+                        s = -CUDART_INF_F;
+                    block_max = fmaxf(block_max, s);
+                }
+            }
+            const float new_max = fmaxf(running_max, block_max);
+            const float correction = fast_exp2((running_max - new_max) * p.scale_log2);
+            const float offset = new_max * p.scale_log2;
+            // The previous block's P V product: add it, then bring everything to the new maximum.
+            if (j > 0) {
+                ok = mbarrier_wait(o_full, (j - 1) & 1, abort_flag, p.counters, 207);
+                if (!ok)
+                    break;
+                tcgen05_fence_after();
+#pragma unroll
+                for (int c = 0; c < HeadSize / 32; ++c) {
+                    uint32_t r[32];
+                    tmem_load_32x32_async(tmem_o + lane_base + c * 32, r);
+                    tmem_wait_load(r);
+#pragma unroll
+                    for (int i = 0; i < 32; ++i)
+                        o[c * 32 + i] = (o[c * 32 + i] + __uint_as_float(r[i])) * correction;
+                }
+            }
+            // Pass 2: probabilities relative to the new maximum, packed to BF16 pairs in TMEM.
+            float block_sum = 0.f;
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                uint32_t packed[32];
+#pragma unroll
+                for (int c = 0; c < 2; ++c) {
+                    uint32_t r[32];
+                    tmem_load_32x32_async(tmem_s + lane_base + (half * 2 + c) * 32, r);
+                    tmem_wait_load(r);
+#pragma unroll
+                    for (int i = 0; i < 32; i += 2) {
+                        const int k = (half * 2 + c) * 32 + i;
+                        float p0 = fast_exp2(fmaf(__uint_as_float(r[i]), p.scale_log2, -offset));
+                        float p1 = fast_exp2(fmaf(__uint_as_float(r[i + 1]), p.scale_log2, -offset));
+                        if (diagonal) {
+                            p0 = k > row ? 0.f : p0;
+                            p1 = k + 1 > row ? 0.f : p1;
+                        }
+                        block_sum += p0 + p1;
+                        packed[c * 16 + i / 2] = pack_bf16(p0, p1);
+                    }
+                }
+                tmem_store_32x32(tmem_p + lane_base + half * 32, packed);
+            }
+            tmem_wait_store();
+            tcgen05_fence_before();
+            __syncwarp();
+            if (lane == 0)
+                mbarrier_arrive(p_full);
+            running_sum = running_sum * correction + block_sum;
+            running_max = new_max;
+        }
+        if (ok)
+            ok = mbarrier_wait(o_full, (blocks - 1) & 1, abort_flag, p.counters, 208);
+        if (ok) {
+            tcgen05_fence_after();
+            const float inverse = 1.f / running_sum;
+#pragma unroll
+            for (int c = 0; c < HeadSize / 32; ++c) {
+                uint32_t r[32];
+                tmem_load_32x32_async(tmem_o + lane_base + c * 32, r);
+                tmem_wait_load(r);
+#pragma unroll
+                for (int i = 0; i < 32; ++i)
+                    o[c * 32 + i] = (o[c * 32 + i] + __uint_as_float(r[i])) * inverse;
+            }
+            if (position < p.context) {
+                bf16 *out = p.out + (int64_t(row0) + position) * p.width + h * HeadSize;
+#pragma unroll
+                for (int g = 0; g < HeadSize / 8; ++g) {
+                    float v[8];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i)
+                        v[i] = o[g * 8 + i];
+                    store8(out + g * 8, v);
+                }
+                // natural-log sum-exp of the scaled scores
+                p.lse[(int64_t(b) * p.heads + h) * p.context + position] =
+                    (running_max * p.scale_log2 + log2f(running_sum)) * 0.6931471805599453f;
+            }
+        }
+    }
+    __syncthreads();
+    if (*abort_flag)
+        __nanosleep(2000000);
+    tcgen05_fence_before();
+    __syncthreads();
+    if (warp == 1)
+        tmem_dealloc(tmem_base, ForwardTmemColumns);
+}
+
+// ------------------------------------------------------------------------------------------
+// Backward.  Two kernels, both deterministic (no atomics):
+//   dq kernel    : one CTA per 128 query rows, loops over key blocks of 64.  S = Q K^T and
+//                  dP = dO V^T land in tensor memory; thread = query row computes
+//                  dS = P (dP - delta) / sqrt(d) with P = exp(S / sqrt(d) - lse), packs it to BF16 in
+//                  tensor memory, and dQ += dS K accumulates in tensor memory across the loop.
+//   dk/dv kernel : one CTA per 128 keys, loops over query blocks of 64 with everything
+//                  transposed (S^T = K Q^T, dP^T = V dO^T: thread = key row), so P^T and dS^T are
+//                  A operands in tensor memory for dV += P^T dO and dK += dS^T Q.
+// Both keep 256 TMEM columns and under 100 KB of shared memory, so two CTAs share an SM.
+// ------------------------------------------------------------------------------------------
+constexpr int BackwardThreads = 192, BackwardTmemColumns = 256, HalfTileBytes = 64 * HeadSize * 2; // 8 KB
+constexpr int DqShared = 2 * TileBytes + 4 * HalfTileBytes + 1024 + 256;      // Q, dO + 2 x (K, V) blocks
+constexpr int DkvShared = 2 * TileBytes + 4 * HalfTileBytes + 1024 + 1024 + 256; // K, V + 2 x (Q, dO) + statistics
+
+struct BackwardParams {
+    bf16 *dqkv;
+    const float *lse, *delta;
+    int batch, context, heads, width, tiles;
+    float scale, scale_log2;
+    StepCounters *counters;
+};
+
+__device__ __forceinline__ void load_columns_64(uint32_t address, uint32_t (&a)[32], uint32_t (&b)[32]) {
+    tmem_load_32x32_async(address, a);
+    tmem_load_32x32_async(address + 32, b);
+}
+
+__global__ void __launch_bounds__(BackwardThreads, 2)
+flash_dq_kernel(const __grid_constant__ CUtensorMap map_qkv128, const __grid_constant__ CUtensorMap map_qkv64,
+                const __grid_constant__ CUtensorMap map_do128, BackwardParams p) {
+    extern __shared__ uint8_t raw_shared[];
+    const uint32_t base = (smem_address(raw_shared) + 1023u) & ~1023u;
+    uint8_t *aligned = raw_shared + (base - smem_address(raw_shared));
+    uint64_t *barriers = reinterpret_cast<uint64_t *>(aligned + 2 * TileBytes + 4 * HalfTileBytes);
+    const uint32_t qdo_full = smem_address(barriers), kv_full0 = qdo_full + 8, kv_empty0 = kv_full0 + 16,
+                   s_full = kv_empty0 + 16, ds_full = s_full + 8, dq_done = ds_full + 8;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(barriers + 8);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+    const uint32_t smem_q = base, smem_do = base + TileBytes, smem_kv = base + 2 * TileBytes;
+
+    const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+    const int pairs = p.batch * p.heads;
+    const int tile = p.tiles - 1 - int(blockIdx.x / pairs);
+    const int bh = blockIdx.x % pairs, b = bh / p.heads, h = bh % p.heads;
+    const int row0 = b * p.context;
+    const int last_key = min(p.context, (tile + 1) * BlockM); // keys 0..last_key-1 can be attended
+    const int blocks = (last_key + 63) / 64;
+
+    if (threadIdx.x == 0) {
+        mbarrier_init(qdo_full, 1);
+        for (int s = 0; s < 2; ++s) {
+            mbarrier_init(kv_full0 + 8 * s, 1);
+            mbarrier_init(kv_empty0 + 8 * s, 1);
+        }
+        mbarrier_init(s_full, 1);
+        mbarrier_init(ds_full, 4);
+        mbarrier_init(dq_done, 1);
+        *abort_flag = 0;
+        fence_barrier_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_address(tmem_slot), BackwardTmemColumns);
+        tmem_relinquish();
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    const uint32_t tmem_s = tmem_base, tmem_dp = tmem_base + 64, tmem_dq = tmem_base + 128; // dS packs into S
+
+    if (warp == 0) {
+        if (elect_one()) {
+            mbarrier_expect_tx(qdo_full, 2 * TileBytes);
+            tma_load_3d(smem_q, &map_qkv128, h * HeadSize, row0 + tile * BlockM, 0, qdo_full);
+            tma_load_3d(smem_do, &map_do128, h * HeadSize, row0 + tile * BlockM, 0, qdo_full);
+            for (int j = 0; j < blocks; ++j) {
+                const int stage = j & 1;
+                if (!mbarrier_wait(kv_empty0 + 8 * stage, ((j >> 1) & 1) ^ 1, abort_flag, p.counters, 301))
+                    break;
+                const uint32_t bar = kv_full0 + 8 * stage, dst = smem_kv + stage * 2 * HalfTileBytes;
+                mbarrier_expect_tx(bar, 2 * HalfTileBytes);
+                tma_load_3d(dst, &map_qkv64, p.width + h * HeadSize, row0 + j * 64, 0, bar);
+                tma_load_3d(dst + HalfTileBytes, &map_qkv64, 2 * p.width + h * HeadSize, row0 + j * 64, 0, bar);
+            }
+        }
+    } else if (warp == 1) {
+        if (elect_one()) {
+            const uint32_t idesc_s = instruction_descriptor(BlockM, 64, 0, 0);
+            const uint32_t idesc_dq = instruction_descriptor(BlockM, HeadSize, 0, 1);
+            bool ok = mbarrier_wait(qdo_full, 0, abort_flag, p.counters, 302);
+            for (int j = 0; j < blocks && ok; ++j) {
+                const uint32_t k_tile = smem_kv + (j & 1) * 2 * HalfTileBytes, v_tile = k_tile + HalfTileBytes;
+                ok = mbarrier_wait(kv_full0 + 8 * (j & 1), (j >> 1) & 1, abort_flag, p.counters, 303);
+                if (!ok)
+                    break;
+                tcgen05_fence_after();
+#pragma unroll
+                for (int ks = 0; ks < HeadSize / 16; ++ks)
+                    tcgen05_mma_bf16(tmem_s, smem_descriptor(smem_q + ks * 32, 16, 1024),
+                                     smem_descriptor(k_tile + ks * 32, 16, 1024), idesc_s, ks > 0);
+#pragma unroll
+                for (int ks = 0; ks < HeadSize / 16; ++ks)
+                    tcgen05_mma_bf16(tmem_dp, smem_descriptor(smem_do + ks * 32, 16, 1024),
+                                     smem_descriptor(v_tile + ks * 32, 16, 1024), idesc_s, ks > 0);
+                tcgen05_commit(s_full);
+                ok = mbarrier_wait(ds_full, j & 1, abort_flag, p.counters, 304);
+                if (!ok)
+                    break;
+                tcgen05_fence_after();
+#pragma unroll
+                for (int ks = 0; ks < 64 / 16; ++ks) // dQ += dS K_j: four 16-key steps
+                    tcgen05_mma_bf16_ts(tmem_dq, tmem_s + ks * 8, smem_descriptor(k_tile + ks * 2048, 8192, 1024),
+                                        idesc_dq, (j > 0 || ks > 0) ? 1u : 0u);
+                tcgen05_commit(kv_empty0 + 8 * (j & 1));
+            }
+            if (ok)
+                tcgen05_commit(dq_done);
+        }
+    } else {
+        const int quarter = warp % 4;
+        const int row = quarter * 32 + lane, position = tile * BlockM + row;
+        const uint32_t lane_base = uint32_t(quarter * 32) << 16;
+        const bool valid = position < p.context;
+        const int64_t stat = (int64_t(b) * p.heads + h) * p.context + position;
+        const float lse2 = valid ? p.lse[stat] * 1.4426950408889634f : 0.f;
+        const float delta = valid ? p.delta[stat] : 0.f;
+        bool ok = true;
+        for (int j = 0; j < blocks; ++j) {
+            ok = mbarrier_wait(s_full, j & 1, abort_flag, p.counters, 305);
+            if (!ok)
+                break;
+            tcgen05_fence_after();
+            uint32_t s0[32], s1[32], d0[32], d1[32], packed[32];
+            load_columns_64(tmem_s + lane_base, s0, s1);
+            load_columns_64(tmem_dp + lane_base, d0, d1);
+            tmem_wait_load(s0);
+            tmem_wait_load(s1);
+            tmem_wait_load(d0);
+            tmem_wait_load(d1);
+            const bool masked_block = (j + 1) * 64 > position; // some keys of this block lie after the query
+#pragma unroll
+            for (int i = 0; i < 32; i += 2) {
+                float v[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const uint32_t sr = u < 2 ? s0[i + u] : s1[i + u - 2], dr = u < 2 ? d0[i + u] : d1[i + u - 2];
+                    const int key = j * 64 + (u < 2 ? i + u : 32 + i + u - 2);
+                    float prob = fast_exp2(fmaf(__uint_as_float(sr), p.scale_log2, -lse2));
+                    float ds = prob * (__uint_as_float(dr) - delta) * p.scale;
+                    v[u] = (masked_block && key > position) || !valid ? 0.f : ds;
+                }
+                packed[i / 2] = pack_bf16(v[0], v[1]);
+                packed[16 + i / 2] = pack_bf16(v[2], v[3]);
+            }
+            tmem_store_32x32(tmem_s + lane_base, packed);
+            tmem_wait_store();
+            tcgen05_fence_before();
+            __syncwarp();
+            if (lane == 0)
+                mbarrier_arrive(ds_full);
+        }
+        if (ok)
+            ok = mbarrier_wait(dq_done, 0, abort_flag, p.counters, 306);
+        if (ok) {
+            tcgen05_fence_after();
+            uint32_t a[32], c[32];
+            load_columns_64(tmem_dq + lane_base, a, c);
+            tmem_wait_load(a);
+            tmem_wait_load(c);
+            if (valid) {
+                bf16 *out = p.dqkv + (int64_t(row0) + position) * 3 * p.width + h * HeadSize;
+#pragma unroll
+                for (int g = 0; g < 8; ++g) {
+                    float v[8];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i)
+                        v[i] = __uint_as_float(g < 4 ? a[g * 8 + i] : c[(g - 4) * 8 + i]);
+                    store8(out + g * 8, v);
+                }
+            }
+        }
+    }
+    __syncthreads();
+    if (*abort_flag)
+        __nanosleep(2000000);
+    tcgen05_fence_before();
+    __syncthreads();
+    if (warp == 1)
+        tmem_dealloc(tmem_base, BackwardTmemColumns);
+}
+
+__global__ void __launch_bounds__(BackwardThreads, 2)
+flash_dkv_kernel(const __grid_constant__ CUtensorMap map_qkv128, const __grid_constant__ CUtensorMap map_qkv64,
+                 const __grid_constant__ CUtensorMap map_do64, BackwardParams p) {
+    extern __shared__ uint8_t raw_shared[];
+    const uint32_t base = (smem_address(raw_shared) + 1023u) & ~1023u;
+    uint8_t *aligned = raw_shared + (base - smem_address(raw_shared));
+    float *statistics = reinterpret_cast<float *>(aligned + 2 * TileBytes + 4 * HalfTileBytes); // [2][lse 64 | delta 64]
+    uint64_t *barriers = reinterpret_cast<uint64_t *>(aligned + 2 * TileBytes + 4 * HalfTileBytes + 1024);
+    const uint32_t kv_full = smem_address(barriers), qdo_full0 = kv_full + 8, qdo_empty0 = qdo_full0 + 16,
+                   s_full = qdo_empty0 + 16, pd_full = s_full + 8, acc_done = pd_full + 8;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(barriers + 8);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+    const uint32_t smem_k = base, smem_v = base + TileBytes, smem_qdo = base + 2 * TileBytes;
+
+    const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+    const int pairs = p.batch * p.heads;
+    const int tile = int(blockIdx.x / pairs); // key tile; early tiles have the most query blocks
+    const int bh = blockIdx.x % pairs, b = bh / p.heads, h = bh % p.heads;
+    const int row0 = b * p.context;
+    const int first_block = tile * 2, query_blocks = (p.context + 63) / 64; // query blocks first_block .. query_blocks-1
+    const int blocks = query_blocks - first_block;
+
+    if (threadIdx.x == 0) {
+        mbarrier_init(kv_full, 1);
+        for (int s = 0; s < 2; ++s) {
+            mbarrier_init(qdo_full0 + 8 * s, 1);
+            mbarrier_init(qdo_empty0 + 8 * s, 1);
+        }
+        mbarrier_init(s_full, 1);
+        mbarrier_init(pd_full, 4);
+        mbarrier_init(acc_done, 1);
+        *abort_flag = 0;
+        fence_barrier_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_address(tmem_slot), BackwardTmemColumns);
+        tmem_relinquish();
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    // S^T 0..63 (P^T packs into 0..31) | dP^T 64..127 (dS^T packs into 64..95) | dV 128..191 | dK 192..255
+    const uint32_t tmem_s = tmem_base, tmem_dp = tmem_base + 64, tmem_dv = tmem_base + 128, tmem_dk = tmem_base + 192;
+
+    if (warp == 0) {
+        if (elect_one()) {
+            mbarrier_expect_tx(kv_full, 2 * TileBytes);
+            tma_load_3d(smem_k, &map_qkv128, p.width + h * HeadSize, row0 + tile * BlockN, 0, kv_full);
+            tma_load_3d(smem_v, &map_qkv128, 2 * p.width + h * HeadSize, row0 + tile * BlockN, 0, kv_full);
+            for (int i = 0; i < blocks; ++i) {
+                const int stage = i & 1;
+                if (!mbarrier_wait(qdo_empty0 + 8 * stage, ((i >> 1) & 1) ^ 1, abort_flag, p.counters, 311))
+                    break;
+                const uint32_t bar = qdo_full0 + 8 * stage, dst = smem_qdo + stage * 2 * HalfTileBytes;
+                mbarrier_expect_tx(bar, 2 * HalfTileBytes);
+                tma_load_3d(dst, &map_qkv64, h * HeadSize, row0 + (first_block + i) * 64, 0, bar);
+                tma_load_3d(dst + HalfTileBytes, &map_do64, h * HeadSize, row0 + (first_block + i) * 64, 0, bar);
+            }
+        }
+    } else if (warp == 1) {
+        if (elect_one()) {
+            const uint32_t idesc_s = instruction_descriptor(BlockN, 64, 0, 0);
+            const uint32_t idesc_acc = instruction_descriptor(BlockN, HeadSize, 0, 1);
+            bool ok = mbarrier_wait(kv_full, 0, abort_flag, p.counters, 312);
+            for (int i = 0; i < blocks && ok; ++i) {
+                const uint32_t q_tile = smem_qdo + (i & 1) * 2 * HalfTileBytes, do_tile = q_tile + HalfTileBytes;
+                ok = mbarrier_wait(qdo_full0 + 8 * (i & 1), (i >> 1) & 1, abort_flag, p.counters, 313);
+                if (!ok)
+                    break;
+                tcgen05_fence_after();
+#pragma unroll
+                for (int ks = 0; ks < HeadSize / 16; ++ks) // S^T = K Q_i^T
+                    tcgen05_mma_bf16(tmem_s, smem_descriptor(smem_k + ks * 32, 16, 1024),
+                                     smem_descriptor(q_tile + ks * 32, 16, 1024), idesc_s, ks > 0);
+#pragma unroll
+                for (int ks = 0; ks < HeadSize / 16; ++ks) // dP^T = V dO_i^T
+                    tcgen05_mma_bf16(tmem_dp, smem_descriptor(smem_v + ks * 32, 16, 1024),
+                                     smem_descriptor(do_tile + ks * 32, 16, 1024), idesc_s, ks > 0);
+                tcgen05_commit(s_full);
+                ok = mbarrier_wait(pd_full, i & 1, abort_flag, p.counters, 314);
+                if (!ok)
+                    break;
+                tcgen05_fence_after();
+#pragma unroll
+                for (int ks = 0; ks < 64 / 16; ++ks) // dV += P^T dO_i
+                    tcgen05_mma_bf16_ts(tmem_dv, tmem_s + ks * 8, smem_descriptor(do_tile + ks * 2048, 8192, 1024),
+                                        idesc_acc, (i > 0 || ks > 0) ? 1u : 0u);
+#pragma unroll
+                for (int ks = 0; ks < 64 / 16; ++ks) // dK += dS^T Q_i
+                    tcgen05_mma_bf16_ts(tmem_dk, tmem_dp + ks * 8, smem_descriptor(q_tile + ks * 2048, 8192, 1024),
+                                        idesc_acc, (i > 0 || ks > 0) ? 1u : 0u);
+                tcgen05_commit(qdo_empty0 + 8 * (i & 1));
+            }
+            if (ok)
+                tcgen05_commit(acc_done);
+        }
+    } else {
+        const int quarter = warp % 4;
+        const int row = quarter * 32 + lane, key = tile * BlockN + row; // key position inside the sequence
+        const uint32_t lane_base = uint32_t(quarter * 32) << 16;
+        const int t128 = threadIdx.x - 64; // 0..127 among the compute threads
+        const float *lse = p.lse + (int64_t(b) * p.heads + h) * p.context;
+        const float *delta = p.delta + (int64_t(b) * p.heads + h) * p.context;
+        bool ok = true;
+        for (int i = 0; i < blocks; ++i) {
+            const int q0 = (first_block + i) * 64;
+            float *stats = statistics + (i & 1) * 128;
+            { // one statistic per thread: lse (scaled to base 2) for 64 queries, then delta
+                const int q = q0 + (t128 & 63);
+                float value = 0.f;
+                if (q < p.context)
+                    value = t128 < 64 ? lse[q] * 1.4426950408889634f : delta[q];
+                stats[t128] = value;
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            bool ready = mbarrier_wait(s_full, i & 1, abort_flag, p.counters, 315);
+            // all four warps meet at the named barrier above every iteration: leave together
+            uint32_t all_ready;
+            asm volatile("{\n\t.reg .pred a, c;\n\tsetp.ne.u32 a, %1, 0;\n\tbar.red.and.pred c, 2, 128, a;\n\t"
+                         "selp.u32 %0, 1, 0, c;\n\t}"
+                         : "=r"(all_ready)
+                         : "r"(uint32_t(ready))
+                         : "memory");
+            ok = all_ready != 0;
+            if (!ok)
+                break;
+            tcgen05_fence_after();
+            uint32_t s0[32], s1[32], d0[32], d1[32], pp[32], pd[32];
+            load_columns_64(tmem_s + lane_base, s0, s1);
+            load_columns_64(tmem_dp + lane_base, d0, d1);
+            tmem_wait_load(s0);
+            tmem_wait_load(s1);
+            tmem_wait_load(d0);
+            tmem_wait_load(d1);
+            const bool edge = q0 < key + 1 || q0 + 64 > p.context; // causal diagonal or ragged end
+#pragma unroll
+            for (int c = 0; c < 32; c += 2) {
+                float pv[4], dv[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const int col = u < 2 ? c + u : 32 + c + u - 2;
+                    const uint32_t sr = u < 2 ? s0[c + u] : s1[c + u - 2], dr = u < 2 ? d0[c + u] : d1[c + u - 2];
+                    float prob = fast_exp2(fmaf(__uint_as_float(sr), p.scale_log2, -stats[col]));
+                    if (edge && (q0 + col < key || q0 + col >= p.context))
+                        prob = 0.f;
+                    pv[u] = prob;
+                    dv[u] = prob * (__uint_as_float(dr) - stats[64 + col]) * p.scale;
+                }
+                pp[c / 2] = pack_bf16(pv[0], pv[1]);
+                pp[16 + c / 2] = pack_bf16(pv[2], pv[3]);
+                pd[c / 2] = pack_bf16(dv[0], dv[1]);
+                pd[16 + c / 2] = pack_bf16(dv[2], dv[3]);
+            }
+            tmem_store_32x32(tmem_s + lane_base, pp);
+            tmem_store_32x32(tmem_dp + lane_base, pd);
+            tmem_wait_store();
+            tcgen05_fence_before();
+            __syncwarp();
+            if (lane == 0)
+                mbarrier_arrive(pd_full);
+        }
+        if (ok)
+            ok = mbarrier_wait(acc_done, 0, abort_flag, p.counters, 316);
+        if (ok) {
+            tcgen05_fence_after();
+#pragma unroll
+            for (int which = 0; which < 2; ++which) { // dK then dV
+                uint32_t a[32], c[32];
+                load_columns_64((which == 0 ? tmem_dk : tmem_dv) + lane_base, a, c);
+                tmem_wait_load(a);
+                tmem_wait_load(c);
+                if (key < p.context) {
+                    bf16 *out = p.dqkv + (int64_t(row0) + key) * 3 * p.width + (which + 1) * p.width + h * HeadSize;
+#pragma unroll
+                    for (int g = 0; g < 8; ++g) {
+                        float v[8];
+#pragma unroll
+                        for (int e = 0; e < 8; ++e)
+                            v[e] = __uint_as_float(g < 4 ? a[g * 8 + e] : c[(g - 4) * 8 + e]);
+                        store8(out + g * 8, v);
+                    }
+                }
+            }
+        }
+    }
+    __syncthreads();
+    if (*abort_flag)
+        __nanosleep(2000000);
+    tcgen05_fence_before();
+    __syncthreads();
+    if (warp == 1)
+        tmem_dealloc(tmem_base, BackwardTmemColumns);
+}
+
+} // namespace
+
+bool flash_attention_supported(int width, int heads) {
+    return heads > 0 && width == heads * HeadSize;
+}
+
+void launch_flash_attention_forward(const void *qkv, void *out, float *lse, int batch, int context, int heads,
+                                    StepCounters *counters, cudaStream_t s) {
+    static bool configured[64] = {};
+    int device = 0;
+    CHECK_CUDA(cudaGetDevice(&device));
+    if (device < 64 && !configured[device]) {
+        CHECK_CUDA(cudaFuncSetAttribute(flash_forward_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        ForwardShared));
+        configured[device] = true;
+    }
+    const int width = heads * HeadSize;
+    ForwardParams p{};
+    p.out = static_cast<bf16 *>(out), p.lse = lse;
+    p.batch = batch, p.context = context, p.heads = heads, p.width = width;
+    p.tiles = (context + BlockM - 1) / BlockM;
+    p.scale_log2 = 1.4426950408889634f / sqrtf(float(HeadSize));
+    p.counters = counters;
+    CUtensorMap map = make_map_bf16(qkv, uint64_t(3) * width, uint64_t(batch) * context, 1, uint64_t(3) * width, 0,
+                                    HeadSize, 128);
+    flash_forward_kernel<<<batch * heads * p.tiles, ForwardThreads, ForwardShared, s>>>(map, p);
+    CHECK_CUDA(cudaGetLastError());
+}
+
+void launch_flash_attention_backward(const void *qkv, const void *dout, const float *lse, const float *delta,
+                                     void *dqkv, int batch, int context, int heads, StepCounters *counters,
+                                     cudaStream_t s) {
+    static bool configured[64] = {};
+    int device = 0;
+    CHECK_CUDA(cudaGetDevice(&device));
+    if (device < 64 && !configured[device]) {
+        CHECK_CUDA(cudaFuncSetAttribute(flash_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DqShared));
+        CHECK_CUDA(cudaFuncSetAttribute(flash_dkv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DkvShared));
+        configured[device] = true;
+    }
+    const int width = heads * HeadSize;
+    BackwardParams p{};
+    p.dqkv = static_cast<bf16 *>(dqkv), p.lse = lse, p.delta = delta;
+    p.batch = batch, p.context = context, p.heads = heads, p.width = width;
+    p.tiles = (context + BlockM - 1) / BlockM;
+    p.scale = 1.f / sqrtf(float(HeadSize));
+    p.scale_log2 = 1.4426950408889634f * p.scale;
+    p.counters = counters;
+    const uint64_t rows = uint64_t(batch) * context;
+    CUtensorMap qkv128 = make_map_bf16(qkv, uint64_t(3) * width, rows, 1, uint64_t(3) * width, 0, HeadSize, 128);
+    CUtensorMap qkv64 = make_map_bf16(qkv, uint64_t(3) * width, rows, 1, uint64_t(3) * width, 0, HeadSize, 64);
+    CUtensorMap do128 = make_map_bf16(dout, width, rows, 1, width, 0, HeadSize, 128);
+    CUtensorMap do64 = make_map_bf16(dout, width, rows, 1, width, 0, HeadSize, 64);
+    const int grid = batch * heads * p.tiles;
+    flash_dkv_kernel<<<grid, BackwardThreads, DkvShared, s>>>(qkv128, qkv64, do64, p);
+    flash_dq_kernel<<<grid, BackwardThreads, DqShared, s>>>(qkv128, qkv64, do128, p);
+    CHECK_CUDA(cudaGetLastError());
+}

@@ -356,7 +356,12 @@ void Engine::forward(bool want_gradient, bool dump_logits) {
             run(FAttentionForward, [&] { launch_argmax_attention(act, at, stream); });
         } else {
             SoftmaxAttentionArgs at{a.qkv, a.attended, a.lse, B, T, W, H};
-            run(FAttentionForward, [&] { launch_softmax_attention(act, at, stream); });
+            run(FAttentionForward, [&] {
+                if (tensor_cores && act == Dtype::BF16 && flash_attention_supported(W, H))
+                    launch_flash_attention_forward(a.qkv, a.attended, a.lse, B, T, H, counters, stream);
+                else
+                    launch_softmax_attention(act, at, stream);
+            });
         }
         GemmArgs proj;
         proj.a = a.attended, proj.a_row = W, proj.b = weight(p.attention), proj.b_row = W, proj.c = a.middle;
@@ -479,7 +484,15 @@ void Engine::backward() {
             run(FAttentionBackward, [&] { launch_argmax_attention_backward(act, at, stream); });
         } else {
             SoftmaxAttentionBackwardArgs at{a.qkv, a.attended, dbranch, a.lse, attention_scratch, dqkv, B, T, W, H};
-            run(FAttentionBackward, [&] { launch_softmax_attention_backward(act, at, stream); });
+            run(FAttentionBackward, [&] {
+                if (tensor_cores && act == Dtype::BF16 && flash_attention_supported(W, H)) {
+                    launch_attention_delta(act, at, stream);
+                    launch_flash_attention_backward(a.qkv, dbranch, a.lse, attention_scratch, dqkv, B, T, H, counters,
+                                                    stream);
+                } else {
+                    launch_softmax_attention_backward(act, at, stream);
+                }
+            });
         }
         if (c.rope == TG_ROPE_PARTIAL)
             run(FMisc, [&] { launch_rope(act, dqkv, M, T, W, H, true, stream); });

@@ -98,6 +98,17 @@ struct SoftmaxAttentionBackwardArgs {
 };
 void launch_softmax_attention_backward(Dtype t, const SoftmaxAttentionBackwardArgs &a, cudaStream_t s);
 
+// ---- causal softmax attention on tcgen05 (BF16, head size 64) ----
+bool flash_attention_supported(int width, int heads);
+void launch_flash_attention_forward(const void *qkv, void *out, float *lse, int batch, int context, int heads,
+                                    StepCounters *counters, cudaStream_t s);
+
+// delta = rowsum(dout * out) into a.delta; lse/dqkv of `a` are not touched.
+void launch_attention_delta(Dtype t, const SoftmaxAttentionBackwardArgs &a, cudaStream_t s);
+void launch_flash_attention_backward(const void *qkv, const void *dout, const float *lse, const float *delta,
+                                     void *dqkv, int batch, int context, int heads, StepCounters *counters,
+                                     cudaStream_t s);
+
 // ---- MLP activations (reference cuda/ops.cuh:118-144) ----
 // wide: [tokens, 2*hidden] = gate | up.  out: [tokens, hidden].
 void launch_swiglu(Dtype t, const void *wide, void *out, int tokens, int hidden, cudaStream_t s);

@@ -258,10 +258,15 @@ int tg_ex_attention_forward(const void *qkv, void *out, float *lse, int batch, i
                             int tensor_cores, void *stream) {
     return guarded([&] {
         require_sm100();
-        if (tensor_cores)
-            throw std::runtime_error("tensor-core attention is not available in this build");
-        SoftmaxAttentionArgs a{qkv, out, lse, batch, context, heads * d_head, heads};
-        launch_softmax_attention(Dtype::BF16, a, static_cast<cudaStream_t>(stream));
+        if (tensor_cores) {
+            if (!flash_attention_supported(heads * d_head, heads))
+                throw std::runtime_error("tensor-core attention needs a head size of 64");
+            launch_flash_attention_forward(qkv, out, lse, batch, context, heads, nullptr,
+                                           static_cast<cudaStream_t>(stream));
+        } else {
+            SoftmaxAttentionArgs a{qkv, out, lse, batch, context, heads * d_head, heads};
+            launch_softmax_attention(Dtype::BF16, a, static_cast<cudaStream_t>(stream));
+        }
         CHECK_CUDA(cudaGetLastError());
     });
 }
@@ -269,13 +274,19 @@ int tg_ex_attention_backward(const void *qkv, const void *out, const void *dout,
                              int batch, int context, int heads, int d_head, int tensor_cores, void *stream) {
     return guarded([&] {
         require_sm100();
-        if (tensor_cores)
-            throw std::runtime_error("tensor-core attention is not available in this build");
+        if (tensor_cores && !flash_attention_supported(heads * d_head, heads))
+            throw std::runtime_error("tensor-core attention needs a head size of 64");
         float *delta = nullptr;
         CHECK_CUDA(cudaMallocAsync(&delta, size_t(batch) * heads * context * sizeof(float),
                                    static_cast<cudaStream_t>(stream)));
         SoftmaxAttentionBackwardArgs a{qkv, out, dout, lse, delta, dqkv, batch, context, heads * d_head, heads};
-        launch_softmax_attention_backward(Dtype::BF16, a, static_cast<cudaStream_t>(stream));
+        if (tensor_cores) {
+            launch_attention_delta(Dtype::BF16, a, static_cast<cudaStream_t>(stream));
+            launch_flash_attention_backward(qkv, dout, lse, delta, dqkv, batch, context, heads, nullptr,
+                                            static_cast<cudaStream_t>(stream));
+        } else {
+            launch_softmax_attention_backward(Dtype::BF16, a, static_cast<cudaStream_t>(stream));
+        }
         CHECK_CUDA(cudaFreeAsync(delta, static_cast<cudaStream_t>(stream)));
         CHECK_CUDA(cudaGetLastError());
     });
