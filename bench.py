@@ -191,15 +191,17 @@ def main() -> None:
     ex = ConfigEx.gpt(base, w["width"], w["heads"], w["hidden"], world=world, rank=rank, flags=args.flags)
     if world > 1:
         import torch.distributed as dist
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-        ident = torch.zeros(128, dtype=torch.uint8, device="cuda")
+        backend = os.environ.get("BENCH_DIST_BACKEND", "nccl")
+        dist.init_process_group(backend)
+        ident = torch.zeros(128, dtype=torch.uint8, device="cuda" if backend == "nccl" else "cpu")
         if rank == 0:
             host = np.zeros(128, np.uint8)
             if lib.tg_ex_nccl_unique_id(host.ctypes.data) < 0:
                 raise SystemExit(lib.tg_error().decode())
             ident.copy_(torch.from_numpy(host))
         dist.broadcast(ident, 0)
-        C.memmove(ex.nccl_id, ident.cpu().numpy().ctypes.data, 128)
+        ident_host = np.ascontiguousarray(ident.cpu().numpy())  # keep alive across the copy
+        C.memmove(ex.nccl_id, ident_host.ctypes.data, 128)
 
     data = markov_bytes(8 << 20, seed=0)
     engine = Native(ex)
@@ -228,7 +230,7 @@ def main() -> None:
     clocks = sampler.stop() if sampler else None
     last_loss = float(engine.training_losses(args.steps)[-1].mean())
     if world > 1:
-        t = torch.tensor([milliseconds], device="cuda", dtype=torch.float64)
+        t = torch.tensor([milliseconds], device=ident.device, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         milliseconds = float(t.item())
     tokens_per_step = w["batch"] * w["context"] * world
@@ -252,7 +254,7 @@ def main() -> None:
     barrier()
     e2e_seconds = time.perf_counter() - start
     if world > 1:
-        t = torch.tensor([e2e_seconds], device="cuda", dtype=torch.float64)
+        t = torch.tensor([e2e_seconds], device=ident.device, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_seconds = float(t.item())
     e2e_value = tokens_per_step * e2e_steps / e2e_seconds

@@ -164,7 +164,75 @@ template <class T> __global__ void __launch_bounds__(256) norm_kernel(NormArgs a
         store8(y + c, out);
     }
 }
+// Widths of 256..1024 in steps of 256: the row lives in registers (one 128-bit load per 256
+// columns and lane), so x is read once; scale and bias are read once per thread.
+template <int V> __device__ __forceinline__ void row_moments(int kind, const float (&x)[V][8], int width,
+                                                            float &mean, float &inv) {
+    float sum = 0, squares = 0;
+#pragma unroll
+    for (int v = 0; v < V; ++v)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            sum += x[v][j];
+            squares += x[v][j] * x[v][j];
+        }
+    if (kind == TG_NORM_RMS) {
+        mean = 0;
+        inv = rsqrtf(warp_sum(squares) / width + 1e-6f);
+        return;
+    }
+    mean = warp_sum(sum) / width;
+    float centred = 0;
+#pragma unroll
+    for (int v = 0; v < V; ++v)
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+            centred += (x[v][j] - mean) * (x[v][j] - mean);
+    inv = rsqrtf(warp_sum(centred) / width + 1e-5f);
+}
+template <class T, int V> __global__ void __launch_bounds__(256) norm_rows_kernel(NormArgs a) {
+    const int lane = threadIdx.x % 32, warps = blockDim.x / 32;
+    float w[V][8], b[V][8];
+#pragma unroll
+    for (int v = 0; v < V; ++v) {
+        const int c = (v * 32 + lane) * 8;
+        load_scale8(a.scale_high, a.scale_low, c, w[v]);
+        if (a.kind == TG_NORM_LAYER)
+            load_scale8(a.bias_high, a.bias_low, c, b[v]);
+    }
+    for (int row = blockIdx.x * warps + threadIdx.x / 32; row < a.rows; row += gridDim.x * warps) {
+        const T *x = (const T *)a.x + int64_t(row) * a.width;
+        T *y = (T *)a.y + int64_t(row) * a.width;
+        float v[V][8];
+#pragma unroll
+        for (int k = 0; k < V; ++k)
+            load8(x + (k * 32 + lane) * 8, v[k]);
+        float mean, inv;
+        row_moments<V>(a.kind, v, a.width, mean, inv);
+#pragma unroll
+        for (int k = 0; k < V; ++k) {
+            float out[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                out[j] = a.kind == TG_NORM_RMS ? v[k][j] * inv * w[k][j] : (v[k][j] - mean) * inv * w[k][j] + b[k][j];
+            store8(y + (k * 32 + lane) * 8, out);
+        }
+    }
+}
+template <class T> static void launch_norm_rows(const NormArgs &a, cudaStream_t s) {
+    const int blocks = blocks_for(a.rows, 8, 148 * 8);
+    switch (a.width / 256) {
+    case 1: norm_rows_kernel<T, 1><<<blocks, 256, 0, s>>>(a); break;
+    case 2: norm_rows_kernel<T, 2><<<blocks, 256, 0, s>>>(a); break;
+    case 3: norm_rows_kernel<T, 3><<<blocks, 256, 0, s>>>(a); break;
+    default: norm_rows_kernel<T, 4><<<blocks, 256, 0, s>>>(a); break;
+    }
+}
 void launch_norm(Dtype t, const NormArgs &a, cudaStream_t s) {
+    if (a.width % 256 == 0 && a.width <= 1024) {
+        DISPATCH(t, launch_norm_rows<T>(a, s));
+        return;
+    }
     DISPATCH(t, (norm_kernel<T><<<blocks_for(a.rows, 8), 256, 0, s>>>(a)));
 }
 
@@ -238,11 +306,101 @@ __global__ void norm_backward_reduce_kernel(const float *partial, float *dscale,
     else
         dbias[c - width] = sum;
 }
+// Register-resident variant for widths 256..1024: x and dy are read once; each lane keeps the
+// scale/bias gradient sums of its own columns over all rows of its warp, warps are summed in
+// order through shared memory, blocks in order by the reduce kernel: deterministic.
+template <class T, int V> __global__ void __launch_bounds__(256, 2) norm_backward_rows_kernel(NormBackwardArgs a) {
+    extern __shared__ float sums[]; // [warps][2][width]
+    const int lane = threadIdx.x % 32, warp = threadIdx.x / 32, warps = blockDim.x / 32;
+    float w[V][8], dw[V][8], db[V][8];
+#pragma unroll
+    for (int v = 0; v < V; ++v) {
+        load_scale8(a.scale_high, a.scale_low, (v * 32 + lane) * 8, w[v]);
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+            dw[v][j] = db[v][j] = 0.f;
+    }
+    for (int row = blockIdx.x * warps + warp; row < a.rows; row += gridDim.x * warps) {
+        const int64_t offset = int64_t(row) * a.width;
+        float x[V][8], g[V][8];
+#pragma unroll
+        for (int v = 0; v < V; ++v) {
+            load8((const T *)a.x + offset + (v * 32 + lane) * 8, x[v]);
+            load8((const T *)a.dy + offset + (v * 32 + lane) * 8, g[v]);
+        }
+        float mean, inv;
+        row_moments<V>(a.kind, x, a.width, mean, inv);
+        float sum_dz = 0, sum_dzz = 0;
+#pragma unroll
+        for (int v = 0; v < V; ++v)
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const float z = (x[v][j] - mean) * inv, dz = g[v][j] * w[v][j];
+                x[v][j] = z; // keep the normalised value
+                sum_dz += dz;
+                sum_dzz += dz * z;
+                dw[v][j] += g[v][j] * z;
+                db[v][j] += g[v][j];
+            }
+        sum_dzz = warp_sum(sum_dzz) / a.width;
+        sum_dz = a.kind == TG_NORM_LAYER ? warp_sum(sum_dz) / a.width : 0.f;
+#pragma unroll
+        for (int v = 0; v < V; ++v) {
+            float out[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                out[j] = (g[v][j] * w[v][j] - sum_dz - x[v][j] * sum_dzz) * inv;
+            if (a.residual_in) {
+                float r[8];
+                load8((const T *)a.residual_in + offset + (v * 32 + lane) * 8, r);
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                    out[j] = r[j] + rounded<T>(out[j]);
+            }
+            store8((T *)a.dx + offset + (v * 32 + lane) * 8, out);
+        }
+    }
+#pragma unroll
+    for (int v = 0; v < V; ++v)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int c = (v * 32 + lane) * 8 + j;
+            sums[(warp * 2) * a.width + c] = dw[v][j];
+            sums[(warp * 2 + 1) * a.width + c] = db[v][j];
+        }
+    __syncthreads();
+    for (int c = threadIdx.x; c < 2 * a.width; c += blockDim.x) {
+        float total = 0;
+        for (int k = 0; k < warps; ++k)
+            total += sums[k * 2 * a.width + c];
+        a.partial[int64_t(blockIdx.x) * 2 * a.width + c] = total;
+    }
+}
+template <class T, int V> static void launch_norm_backward_rows(const NormBackwardArgs &a, cudaStream_t s) {
+    const size_t shared = size_t(8) * 2 * a.width * sizeof(float);
+    if (shared > 48 * 1024)
+        CHECK_CUDA(cudaFuncSetAttribute(norm_backward_rows_kernel<T, V>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        int(shared)));
+    norm_backward_rows_kernel<T, V><<<a.blocks, 256, shared, s>>>(a);
+}
 int norm_backward_blocks(int rows, int sms) {
     return blocks_for(rows, 8, int64_t(sms) * 2);
 }
 void launch_norm_backward(Dtype t, const NormBackwardArgs &a, cudaStream_t s) {
     size_t shared = size_t(2) * a.width * sizeof(float);
+    if (a.width % 256 == 0 && a.width <= 1024) {
+        DISPATCH(t, {
+            switch (a.width / 256) {
+            case 1: launch_norm_backward_rows<T, 1>(a, s); break;
+            case 2: launch_norm_backward_rows<T, 2>(a, s); break;
+            case 3: launch_norm_backward_rows<T, 3>(a, s); break;
+            default: launch_norm_backward_rows<T, 4>(a, s); break;
+            }
+        });
+        norm_backward_reduce_kernel<<<blocks_for(2 * a.width, 128), 128, 0, s>>>(a.partial, a.dscale, a.dbias,
+                                                                               a.width, a.blocks);
+        return;
+    }
     DISPATCH(t, {
         if (shared > 48 * 1024)
             CHECK_CUDA(cudaFuncSetAttribute(norm_backward_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
