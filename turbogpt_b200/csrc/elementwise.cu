@@ -293,18 +293,28 @@ template <class T> __global__ void __launch_bounds__(256) norm_backward_kernel(N
     for (int c = threadIdx.x; c < 2 * a.width; c += blockDim.x)
         a.partial[int64_t(blockIdx.x) * 2 * a.width + c] = sums[c];
 }
-__global__ void norm_backward_reduce_kernel(const float *partial, float *dscale, float *dbias, int width,
-                                            int blocks) {
-    int c = blockIdx.x * blockDim.x + threadIdx.x;
-    if (c >= 2 * width || (c >= width && !dbias))
-        return;
+// 32 columns per block, 8 threads per column: thread g sums blocks g, g+8, ...; the eight
+// sums are added in order.  Same result on every run.
+__global__ void __launch_bounds__(256) norm_backward_reduce_kernel(const float *partial, float *dscale,
+                                                                   float *dbias, int width, int blocks) {
+    __shared__ float sums[8][33];
+    const int lane = threadIdx.x % 32, group = threadIdx.x / 32;
+    const int c = blockIdx.x * 32 + lane;
     float sum = 0;
-    for (int b = 0; b < blocks; ++b)
-        sum += partial[int64_t(b) * 2 * width + c];
-    if (c < width)
-        dscale[c] = sum;
-    else
-        dbias[c - width] = sum;
+    if (c < 2 * width)
+        for (int b = group; b < blocks; b += 8)
+            sum += partial[int64_t(b) * 2 * width + c];
+    sums[group][lane] = sum;
+    __syncthreads();
+    if (group == 0 && c < 2 * width) {
+        float total = 0;
+        for (int g = 0; g < 8; ++g)
+            total += sums[g][lane];
+        if (c < width)
+            dscale[c] = total;
+        else if (dbias)
+            dbias[c - width] = total;
+    }
 }
 // Register-resident variant for widths 256..1024: x and dy are read once; each lane keeps the
 // scale/bias gradient sums of its own columns over all rows of its warp, warps are summed in
@@ -397,8 +407,8 @@ void launch_norm_backward(Dtype t, const NormBackwardArgs &a, cudaStream_t s) {
             default: launch_norm_backward_rows<T, 4>(a, s); break;
             }
         });
-        norm_backward_reduce_kernel<<<blocks_for(2 * a.width, 128), 128, 0, s>>>(a.partial, a.dscale, a.dbias,
-                                                                               a.width, a.blocks);
+        norm_backward_reduce_kernel<<<blocks_for(2 * a.width, 32), 256, 0, s>>>(a.partial, a.dscale, a.dbias,
+                                                                              a.width, a.blocks);
         return;
     }
     DISPATCH(t, {
@@ -407,8 +417,8 @@ void launch_norm_backward(Dtype t, const NormBackwardArgs &a, cudaStream_t s) {
                                             int(shared)));
         norm_backward_kernel<T><<<a.blocks, 256, shared, s>>>(a);
     });
-    norm_backward_reduce_kernel<<<blocks_for(2 * a.width, 128), 128, 0, s>>>(a.partial, a.dscale, a.dbias, a.width,
-                                                                           a.blocks);
+    norm_backward_reduce_kernel<<<blocks_for(2 * a.width, 32), 256, 0, s>>>(a.partial, a.dscale, a.dbias, a.width,
+                                                                          a.blocks);
 }
 
 // ------------------------------------------------------------------------------------------

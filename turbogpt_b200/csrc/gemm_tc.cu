@@ -6,10 +6,16 @@
 // One persistent CTA per SM walks output tiles of 128 x BN (BN = 64..256).  Warp 0 streams
 // operand slices of 64 K-elements with TMA into a ring of 128-byte-swizzled shared-memory
 // stages; warp 1 issues tcgen05.mma (one thread) into one of two TMEM accumulators; warps 2-5
-// drain the other accumulator (tcgen05.ld), apply the epilogue and store, so the epilogue of
-// tile i overlaps the main loop of tile i+1.  Either operand may be K-major (row = 64
-// contiguous K elements) or MN-major (row = 64 contiguous M/N elements for one K index), which
-// covers y = x W^T, dx = dy W and dW = dy^T x on row-major tensors without transposes.
+// drain the other accumulator, so the epilogue of tile i overlaps the main loop of tile i+1.
+// Either operand may be K-major (row = 64 contiguous K elements) or MN-major (row = 64
+// contiguous M/N elements for one K index), which covers y = x W^T, dx = dy W and dW = dy^T x on
+// row-major tensors without transposes.
+//
+// Epilogue: each warp owns 32 rows.  Per 128-byte-wide chunk of its rows it reads the accumulator
+// (tcgen05.ld), optionally combines it with a tile of a second tensor fetched by TMA (residual,
+// pre-activation, or the Newton-Schulz operand), writes the result into a swizzled staging slot
+// and hands the slot to a TMA store: global reads and writes are whole 128-byte lines and the
+// tensor's edges are clipped by the TMA unit.
 //
 // Weight-gradient GEMMs have few output tiles and a very long K; they are split along K, each
 // split writes an FP32 partial tile to a workspace and the last split to finish a tile (an
@@ -22,10 +28,13 @@
 using namespace sm100;
 
 namespace {
-constexpr int BM = 128, BK = 64, MaxBN = 256, Stages = 4;
-constexpr int StageABytes = BM * BK * 2, StageBBytes = MaxBN * BK * 2, StageBytes = StageABytes + StageBBytes;
-constexpr int Threads = 192; // warp 0: TMA, warp 1: MMA, warps 2-5: epilogue
-constexpr int SharedBytes = Stages * StageBytes + 1024 /* alignment slack */ + 256 /* barriers */;
+constexpr int BM = 128, BK = 64, MaxBN = 256, MaxStages = 8;
+constexpr int StageABytes = BM * BK * 2;
+constexpr int EpilogueWarps = 16;
+constexpr int Threads = 64 + 32 * EpilogueWarps; // warp 0: TMA, warp 1: MMA, then the epilogue warps
+constexpr int SlotBytes = 32 * 128; // staging slot: 32 rows x 128 bytes
+constexpr int ControlBytes = 512;   // barriers, TMEM slot, flags
+constexpr int MaxShared = 232448 - 1024; // 227 KB less the runtime's own reservation
 constexpr int TmemColumns = 512;
 
 struct TcParams {
@@ -34,6 +43,8 @@ struct TcParams {
     int a_mn, b_mn;         // operand majorness
     int splits, k_blocks_per_split;
     int epilogue, out_fp32;
+    int stages, slots;      // pipeline depth; (slots unused)
+    int wide;               // C, C2 and R rows are 32-byte aligned: 256-bit epilogue accesses
     void *c, *c2;
     const void *r;
     long long ldc, ldr, c_batch, r_batch;
@@ -43,8 +54,33 @@ struct TcParams {
     StepCounters *counters;
 };
 
+// erf by Abramowitz & Stegun 7.1.26 (|error| < 1.5e-7); the same exponential serves the
+// Gaussian term of the derivative.  z = x / sqrt(2).
+__device__ __forceinline__ void gelu_terms(float x, float &cdf, float &density) {
+    const float z = fabsf(x) * 0.7071067811865475f;
+    const float t = __fdividef(1.f, fmaf(0.3275911f, z, 1.f));
+    const float e = __expf(-z * z);
+    float poly = fmaf(t, 1.061405429f, -1.453152027f);
+    poly = fmaf(t, poly, 1.421413741f);
+    poly = fmaf(t, poly, -0.284496736f);
+    poly = fmaf(t, poly, 0.254829592f);
+    const float tail = 0.5f * poly * t * e;       // 0.5 * erfc(|z|)
+    cdf = x >= 0.f ? 1.f - tail : tail;           // 0.5 * (1 + erf(z))
+    density = 0.3989422804014327f * e;            // exp(-x^2/2) / sqrt(2 pi)
+}
+__device__ __forceinline__ float fast_gelu(float x) {
+    float cdf, density;
+    gelu_terms(x, cdf, density);
+    return x * cdf;
+}
+__device__ __forceinline__ float fast_gelu_derivative(float x) {
+    float cdf, density;
+    gelu_terms(x, cdf, density);
+    return fmaf(x, density, cdf);
+}
+
+// Direct global store of eight consecutive outputs (split-K reduction path only).
 __device__ __forceinline__ void store_group(const TcParams &p, float (&v)[8], long long row, int col, int z) {
-    // Eight consecutive outputs of one row, column multiple of 8.
     const long long ci = z * p.c_batch + row * p.ldc + col, ri = z * p.r_batch + row * p.ldr + col;
     if (p.out_fp32) {
         if (p.epilogue == int(Epilogue::Axpby)) {
@@ -57,51 +93,13 @@ __device__ __forceinline__ void store_group(const TcParams &p, float (&v)[8], lo
         store8((float *)p.c + ci, v);
         return;
     }
-    switch (p.epilogue) {
-    case int(Epilogue::Store):
-        break;
-    case int(Epilogue::Residual): {
-        float r[8];
-        load8((const bf16 *)p.r + ri, r);
-#pragma unroll
-        for (int j = 0; j < 8; ++j)
-            v[j] = rounded<bf16>(v[j]) + r[j];
-        break;
-    }
-    case int(Epilogue::GeluDual): {
-        float act[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            v[j] = rounded<bf16>(v[j]);
-            act[j] = gelu(v[j]);
-        }
-        store8((bf16 *)p.c2 + ci, act);
-        break;
-    }
-    case int(Epilogue::GeluGrad): {
-        float r[8];
-        load8((const bf16 *)p.r + ri, r);
-#pragma unroll
-        for (int j = 0; j < 8; ++j)
-            v[j] = rounded<bf16>(v[j]) * gelu_derivative(r[j]);
-        break;
-    }
-    case int(Epilogue::Axpby): {
-        float r[8];
-        load8((const bf16 *)p.r + ri, r);
-#pragma unroll
-        for (int j = 0; j < 8; ++j)
-            v[j] = p.alpha * v[j] + p.beta * r[j];
-        break;
-    }
-    }
     store8((bf16 *)p.c + ci, v);
 }
 
-// AND of a predicate over the 128 epilogue threads (named barrier 1).
+// AND of a predicate over the 512 epilogue threads (named barrier 1).
 __device__ __forceinline__ bool epilogue_all(bool ok) {
     uint32_t result;
-    asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.u32 p, %1, 0;\n\tbar.red.and.pred q, 1, 128, p;\n\t"
+    asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.u32 p, %1, 0;\n\tbar.red.and.pred q, 1, 512, p;\n\t"
                  "selp.u32 %0, 1, 0, q;\n\t}"
                  : "=r"(result)
                  : "r"(uint32_t(ok))
@@ -109,33 +107,83 @@ __device__ __forceinline__ bool epilogue_all(bool ok) {
     return result != 0;
 }
 
+__device__ __forceinline__ uint4 load_shared16(uint32_t address) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(address));
+    return v;
+}
+__device__ __forceinline__ void store_shared16(uint32_t address, uint4 v) {
+    asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(address), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+                 : "memory");
+}
+// 32 bytes to or from global memory: one 256-bit access when `wide` (32-byte aligned), else two
+// 128-bit accesses; `second` says whether the upper half is inside the tensor.
+__device__ __forceinline__ void load_global32(const void *p, uint32_t (&r)[8], bool wide, bool second) {
+    if (wide) {
+        asm volatile("ld.global.v8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                     : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+                     : "l"(p));
+    } else {
+        uint4 a = *reinterpret_cast<const uint4 *>(p), b = make_uint4(0, 0, 0, 0);
+        if (second)
+            b = *(reinterpret_cast<const uint4 *>(p) + 1);
+        r[0] = a.x, r[1] = a.y, r[2] = a.z, r[3] = a.w, r[4] = b.x, r[5] = b.y, r[6] = b.z, r[7] = b.w;
+    }
+}
+__device__ __forceinline__ void store_global32(void *p, const uint32_t (&r)[8], bool wide, bool second) {
+    if (wide) {
+        asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(p), "r"(r[0]), "r"(r[1]),
+                     "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+                     : "memory");
+    } else {
+        *reinterpret_cast<uint4 *>(p) = make_uint4(r[0], r[1], r[2], r[3]);
+        if (second)
+            *(reinterpret_cast<uint4 *>(p) + 1) = make_uint4(r[4], r[5], r[6], r[7]);
+    }
+}
+__device__ __forceinline__ void unpack8(uint4 u, float (&v)[8]) {
+    const unsigned w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        v[2 * i] = __uint_as_float(w[i] << 16);
+        v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
+}
+
+template <int Kind, bool OutFp32>
 __global__ void __launch_bounds__(Threads, 1)
-gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, TcParams p) {
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+               const __grid_constant__ CUtensorMap map_c, const __grid_constant__ CUtensorMap map_c2,
+               const __grid_constant__ CUtensorMap map_r, TcParams p) {
     extern __shared__ uint8_t raw_shared[];
     const uint32_t base = (smem_address(raw_shared) + 1023u) & ~1023u;
     uint8_t *aligned = raw_shared + (base - smem_address(raw_shared));
-    uint64_t *barriers = reinterpret_cast<uint64_t *>(aligned + Stages * StageBytes);
-    // barrier slots: full[Stages], empty[Stages], tmem_full[2], tmem_empty[2]
-    const uint32_t full0 = smem_address(barriers), empty0 = full0 + 8 * Stages, tfull0 = empty0 + 8 * Stages,
-                   tempty0 = tfull0 + 16;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(barriers + 2 * Stages + 4);
+    const int stage_bytes = StageABytes + p.bn * BK * 2;
+    uint64_t *barriers = reinterpret_cast<uint64_t *>(aligned + p.stages * stage_bytes + 4 * p.slots * SlotBytes);
+    // barrier slots: full[8], empty[8], tmem_full[2], tmem_empty[2], r_full[4 warps][4 slots]
+    const uint32_t full0 = smem_address(barriers), empty0 = full0 + 8 * MaxStages, tfull0 = empty0 + 8 * MaxStages,
+                   tempty0 = tfull0 + 16, rfull0 = tempty0 + 16;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(barriers + 2 * MaxStages + 4 + 16);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
-    __shared__ int last_split_flag[4];
+    volatile int *last_split_flag = reinterpret_cast<volatile int *>(tmem_slot + 2);
 
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
     if (threadIdx.x == 0) {
-        for (int s = 0; s < Stages; ++s) {
+        for (int s = 0; s < p.stages; ++s) {
             mbarrier_init(full0 + 8 * s, 1);
             mbarrier_init(empty0 + 8 * s, 1);
         }
         for (int b = 0; b < 2; ++b) {
             mbarrier_init(tfull0 + 8 * b, 1);
-            mbarrier_init(tempty0 + 8 * b, 4);
+            mbarrier_init(tempty0 + 8 * b, EpilogueWarps);
         }
+        for (int i = 0; i < 16; ++i)
+            mbarrier_init(rfull0 + 8 * i, 1);
         *abort_flag = 0;
         fence_barrier_init();
         prefetch_map(&map_a);
         prefetch_map(&map_b);
+        prefetch_map(&map_c);
     }
     if (warp == 1) {
         tmem_alloc(smem_address(tmem_slot), TmemColumns);
@@ -149,7 +197,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const int m_tiles = (p.m + BM - 1) / BM, n_tiles = (p.n + p.bn - 1) / p.bn;
     const int k_blocks = (p.k + BK - 1) / BK;
     const long long work_items = (long long)m_tiles * n_tiles * p.batch * p.splits;
-    const uint32_t stage_tx = StageABytes + p.bn * BK * 2;
+    const uint32_t stage_tx = stage_bytes;
 
     if (warp == 0) {
         // ---------------- TMA producer ----------------
@@ -167,7 +215,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     ok = mbarrier_wait(empty0 + 8 * stage, phase ^ 1, abort_flag, p.counters, 101);
                     if (!ok)
                         break;
-                    const uint32_t bar = full0 + 8 * stage, sa = base + stage * StageBytes, sb = sa + StageABytes;
+                    const uint32_t bar = full0 + 8 * stage, sa = base + stage * stage_bytes, sb = sa + StageABytes;
                     mbarrier_expect_tx(bar, stage_tx);
                     if (!p.a_mn) {
                         tma_load_3d(sa, &map_a, kb * BK, mt * BM, z, bar);
@@ -181,7 +229,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                         for (int j = 0; j < p.bn / 64; ++j)
                             tma_load_3d(sb + j * 64 * BK * 2, &map_b, nt * p.bn + j * 64, kb * BK, z, bar);
                     }
-                    if (++stage == Stages) {
+                    if (++stage == p.stages) {
                         stage = 0;
                         phase ^= 1;
                     }
@@ -214,7 +262,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     if (!ok)
                         break;
                     tcgen05_fence_after();
-                    const uint32_t sa = base + stage * StageBytes, sb = sa + StageABytes;
+                    const uint32_t sa = base + stage * stage_bytes, sb = sa + StageABytes;
 #pragma unroll
                     for (int ks = 0; ks < BK / 16; ++ks) {
                         uint64_t da = smem_descriptor(sa + ks * a_step, a_lbo, 1024);
@@ -222,7 +270,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                         tcgen05_mma_bf16(accumulator, da, db, instruction, (kb > kb0 || ks > 0) ? 1u : 0u);
                     }
                     tcgen05_commit(empty0 + 8 * stage); // frees the stage once these MMAs have read it
-                    if (++stage == Stages) {
+                    if (++stage == p.stages) {
                         stage = 0;
                         phase ^= 1;
                     }
@@ -237,8 +285,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             }
         }
     } else {
-        // ---------------- epilogue: 4 warps, warp q owns TMEM lanes 32q..32q+31 ----------------
-        const int quarter = warp % 4;
+        // ---------------- epilogue: 16 warps; warps q, q+4, q+8, q+12 share TMEM lanes 32q..32q+31 and
+        // take every fourth 32-column chunk.  Four warps per scheduler hide one another's TMEM,
+        // ALU, SFU and global-load latencies (the epilogue math is a dependent chain per element).
+        constexpr int Shares = EpilogueWarps / 4;
+        const int quarter = warp % 4, share = (warp - 2) / 4;
+        constexpr bool has_r = Kind == int(Epilogue::Residual) || Kind == int(Epilogue::GeluGrad) ||
+                               Kind == int(Epilogue::Axpby);
         int buffer = 0;
         uint32_t buffer_phase = 0;
         for (long long w = blockIdx.x; w < work_items; w += gridDim.x) {
@@ -246,30 +299,96 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             long long t = w / p.splits;
             const int nt = int(t % n_tiles), mt = int(t / n_tiles % m_tiles), z = int(t / n_tiles / m_tiles);
             bool ready = mbarrier_wait(tfull0 + 8 * buffer, buffer_phase, abort_flag, p.counters, 104);
-            if (p.splits > 1) // the four warps meet at named barriers below: leave together or not at all
+            if (p.splits > 1) // the eight warps meet at named barriers below: leave together or not at all
                 ready = epilogue_all(ready);
             if (!ready)
                 break;
             tcgen05_fence_after();
             const long long row = (long long)mt * BM + quarter * 32 + lane;
             const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + buffer * MaxBN;
+            const int tile_columns = min(p.bn, p.n - nt * p.bn);
+            const int chunks = (tile_columns + 31) / 32;
             if (p.splits == 1) {
-                for (int chunk = 0; chunk < p.bn / 32; ++chunk) {
-                    float v[32];
-                    tmem_load_32x32(taddr + chunk * 32, v);
-                    const int col0 = nt * p.bn + chunk * 32;
-                    if (row < p.m) {
+                const bool row_ok = row < p.m;
+                const long long c_row = z * p.c_batch + row * p.ldc, r_row = z * p.r_batch + row * p.ldr;
+                auto process = [&](uint32_t (&acc)[32], int c) {
+                    const int column = nt * p.bn + c * 32;
+                    // Second tensor for this chunk: issue the global loads before waiting on TMEM.
+                    constexpr int Pieces = OutFp32 ? 4 : 2; // 32-byte pieces per 32-column chunk row
+                    constexpr int PieceColumns = 32 / Pieces;
+                    uint32_t rv[has_r ? Pieces : 1][8];
+                    if (has_r && row_ok) {
+                        const char *src = (const char *)p.r + (r_row + column) * (OutFp32 ? 4 : 2);
 #pragma unroll
-                        for (int g = 0; g < 4; ++g) {
-                            if (col0 + g * 8 < p.n) {
-                                float group[8];
+                        for (int g = 0; g < Pieces; ++g)
+                            if (column + g * PieceColumns < p.n)
+                                load_global32(src + g * 32, rv[g], p.wide && column + (g + 1) * PieceColumns <= p.n,
+                                              column + g * PieceColumns + PieceColumns / 2 < p.n);
+                    }
+                    tmem_wait_load(acc);
+                    if (!row_ok)
+                        return;
+                    char *dst = (char *)p.c + (c_row + column) * (OutFp32 ? 4 : 2);
+#pragma unroll
+                    for (int g = 0; g < Pieces; ++g) {
+                        if (column + g * PieceColumns >= p.n)
+                            break;
+                        const bool whole = p.wide && column + (g + 1) * PieceColumns <= p.n;
+                        uint32_t out[8];
+                        if constexpr (OutFp32) {
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) {
+                                float v = __uint_as_float(acc[g * 8 + j]);
+                                if (has_r) // Axpby on FP32
+                                    v = p.alpha * v + p.beta * __uint_as_float(rv[g][j]);
+                                out[j] = __float_as_uint(v);
+                            }
+                        } else {
+                            float v[16], r[16];
+#pragma unroll
+                            for (int j = 0; j < 16; ++j)
+                                v[j] = __uint_as_float(acc[g * 16 + j]);
+                            if (has_r) {
+#pragma unroll
+                                for (int j = 0; j < 8; ++j) {
+                                    r[2 * j] = __uint_as_float(rv[g][j] << 16);
+                                    r[2 * j + 1] = __uint_as_float(rv[g][j] & 0xffff0000u);
+                                }
+                            }
+                            if constexpr (Kind == int(Epilogue::Residual)) {
+#pragma unroll
+                                for (int j = 0; j < 16; ++j)
+                                    v[j] = rounded<bf16>(v[j]) + r[j];
+                            } else if constexpr (Kind == int(Epilogue::GeluDual)) {
+                                uint32_t activated[8];
+#pragma unroll
+                                for (int j = 0; j < 16; ++j)
+                                    v[j] = rounded<bf16>(v[j]);
 #pragma unroll
                                 for (int j = 0; j < 8; ++j)
-                                    group[j] = v[g * 8 + j];
-                                store_group(p, group, row, col0 + g * 8, z);
+                                    activated[j] = pack_bf16(fast_gelu(v[2 * j]), fast_gelu(v[2 * j + 1]));
+                                store_global32((char *)p.c2 + (c_row + column) * 2 + g * 32, activated, whole,
+                                               column + g * 16 + 8 < p.n);
+                            } else if constexpr (Kind == int(Epilogue::GeluGrad)) {
+#pragma unroll
+                                for (int j = 0; j < 16; ++j)
+                                    v[j] = rounded<bf16>(v[j]) * fast_gelu_derivative(r[j]);
+                            } else if constexpr (Kind == int(Epilogue::Axpby)) {
+#pragma unroll
+                                for (int j = 0; j < 16; ++j)
+                                    v[j] = p.alpha * v[j] + p.beta * r[j];
                             }
+#pragma unroll
+                            for (int j = 0; j < 8; ++j)
+                                out[j] = pack_bf16(v[2 * j], v[2 * j + 1]);
                         }
+                        store_global32(dst + g * 32, out, whole, column + g * PieceColumns + PieceColumns / 2 < p.n);
                     }
+                };
+                for (int c = share; c < chunks; c += Shares) {
+                    uint32_t acc[32];
+                    tmem_load_32x32_async(taddr + c * 32, acc);
+                    process(acc, c);
                 }
                 tcgen05_fence_before();
                 __syncwarp();
@@ -279,7 +398,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 // Partial tile to the workspace (padded to whole tiles, so no bounds checks).
                 const long long padded_m = (long long)m_tiles * BM, padded_n = (long long)n_tiles * p.bn;
                 float *partial = p.workspace + ((long long)split * p.batch + z) * padded_m * padded_n;
-                for (int chunk = 0; chunk < p.bn / 32; ++chunk) {
+                for (int chunk = share; chunk < p.bn / 32; chunk += Shares) {
                     float v[32];
                     tmem_load_32x32(taddr + chunk * 32, v);
                     float *out = partial + row * padded_n + nt * p.bn + chunk * 32;
@@ -294,7 +413,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     mbarrier_arrive(tempty0 + 8 * buffer);
                 // Ticket: the split that arrives last reduces the tile in split order.
                 __threadfence();
-                asm volatile("bar.sync 1, 128;" ::: "memory");
+                asm volatile("bar.sync 1, 512;" ::: "memory");
                 if (threadIdx.x == 64) {
                     unsigned ticket = atomicAdd(&p.tickets[t], 1u);
                     int last = ticket == unsigned(p.splits - 1);
@@ -302,33 +421,31 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                         p.tickets[t] = 0; // ready for the next launch
                     last_split_flag[0] = last;
                 }
-                asm volatile("bar.sync 1, 128;" ::: "memory");
+                asm volatile("bar.sync 1, 512;" ::: "memory");
                 if (last_split_flag[0]) {
                     __threadfence();
                     if (row < p.m) {
-                        for (int col = 0; col < p.bn; col += 8) {
-                            const int c = nt * p.bn + col;
-                            if (c >= p.n)
-                                break;
-                            float sum[8] = {};
-                            for (int s = 0; s < p.splits; ++s) {
-                                float v[8];
-                                // L2 only: the partials were written by other SMs.
-                                const float4 *src = reinterpret_cast<const float4 *>(
-                                    p.workspace + ((long long)s * p.batch + z) * padded_m * padded_n +
-                                    row * padded_n + c);
-                                float4 lo = __ldcg(src), hi = __ldcg(src + 1);
-                                v[0] = lo.x, v[1] = lo.y, v[2] = lo.z, v[3] = lo.w;
-                                v[4] = hi.x, v[5] = hi.y, v[6] = hi.z, v[7] = hi.w;
-#pragma unroll
-                                for (int j = 0; j < 8; ++j)
-                                    sum[j] += v[j];
+                        for (int col = share * 32; col < p.bn; col += 32 * Shares) {
+                            for (int sub = 0; sub < 32; sub += 8) {
+                                const int c = nt * p.bn + col + sub;
+                                if (c >= p.n)
+                                    break;
+                                float sum[8] = {};
+                                for (int s = 0; s < p.splits; ++s) {
+                                    // L2 only: the partials were written by other SMs.
+                                    const float4 *src = reinterpret_cast<const float4 *>(
+                                        p.workspace + ((long long)s * p.batch + z) * padded_m * padded_n +
+                                        row * padded_n + c);
+                                    float4 lo = __ldcg(src), hi = __ldcg(src + 1);
+                                    sum[0] += lo.x, sum[1] += lo.y, sum[2] += lo.z, sum[3] += lo.w;
+                                    sum[4] += hi.x, sum[5] += hi.y, sum[6] += hi.z, sum[7] += hi.w;
+                                }
+                                store_group(p, sum, row, c, z);
                             }
-                            store_group(p, sum, row, c, z);
                         }
                     }
                 }
-                asm volatile("bar.sync 1, 128;" ::: "memory"); // last_split_flag is reused next tile
+                asm volatile("bar.sync 1, 512;" ::: "memory"); // last_split_flag is reused next tile
             }
             if (++buffer == 2) {
                 buffer = 0;
@@ -382,7 +499,7 @@ Workspace &workspace_for(size_t partial_bytes, size_t tickets, cudaStream_t s) {
 }
 } // namespace
 
-int gemm_tc_shared_bytes() { return SharedBytes; }
+int gemm_tc_shared_bytes() { return MaxShared; }
 
 bool gemm_tc_supported(const GemmArgs &g) {
     if (g.in != Dtype::BF16)
@@ -401,32 +518,24 @@ bool gemm_tc_supported(const GemmArgs &g) {
         return false;
     if (g.a_batch % 8 || g.b_batch % 8 || g.c_batch % 8 || g.r_batch % 8)
         return false;
-    // An MN-major operand is fetched in 64-wide blocks: its extent must cover whole blocks so a
-    // tile never straddles into the next matrix of a batch.
-    if (!a_k && a_mn && g.m % 8)
-        return false;
     if (g.out == Dtype::FP32 && !(g.epilogue == Epilogue::Store || g.epilogue == Epilogue::Axpby))
         return false;
     return true;
 }
 
 void launch_gemm_tc(const GemmArgs &g, int sms, StepCounters *counters, cudaStream_t s) {
-    static bool configured[64] = {};
-    int device = 0;
-    CHECK_CUDA(cudaGetDevice(&device));
-    if (device < 64 && !configured[device]) {
-        CHECK_CUDA(cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SharedBytes));
-        configured[device] = true;
-    }
     TcParams p{};
     p.m = g.m, p.n = g.n, p.k = g.k, p.batch = g.batch;
     p.a_mn = g.a_col == 1 ? 0 : 1;
     p.b_mn = g.b_col == 1 ? 0 : 1;
+    p.epilogue = int(g.epilogue), p.out_fp32 = g.out == Dtype::FP32;
+    const bool second_tensor = g.epilogue != Epilogue::Store;
+    p.slots = 0;
     const int64_t lda = p.a_mn ? g.a_col : g.a_row, ldb = p.b_mn ? g.b_col : g.b_row;
     const int m_tiles = (g.m + BM - 1) / BM, k_blocks = (g.k + BK - 1) / BK;
     // Tile width and K splits by a small cost model, in clocks per 64-deep K block: the MMA
     // takes bn/2, the shared-memory operand reads (128+bn)/4; a tile adds a fixed drain cost and
-    // every split one pass over the FP32 partial tile.
+    // every split one pass over the FP32 partial tile.  Four staging slots leave room for 192 columns.
     long long best_time = 0;
     p.bn = 0;
     for (int bn : {256, 192, 128, 64}) {
@@ -435,7 +544,7 @@ void launch_gemm_tc(const GemmArgs &g, int sms, StepCounters *counters, cudaStre
         const long long tiles = (long long)m_tiles * ((g.n + bn - 1) / bn) * g.batch;
         const int block_cost = bn / 2 > (128 + bn) / 4 ? bn / 2 : (128 + bn) / 4;
         for (int splits : {1, 2, 3, 4, 6, 8, 12, 16}) {
-            if (splits > 1 && (k_blocks / splits < 8 || tiles * splits > sms))
+            if (splits > 1 && (k_blocks / splits < 8 || tiles * splits > sms || second_tensor))
                 continue;
             const int per = (k_blocks + splits - 1) / splits;
             if (splits > 1 && (k_blocks + per - 1) / per != splits)
@@ -448,11 +557,24 @@ void launch_gemm_tc(const GemmArgs &g, int sms, StepCounters *counters, cudaStre
     }
     const int n_tiles = (g.n + p.bn - 1) / p.bn;
     const long long tiles = (long long)m_tiles * n_tiles * g.batch;
-    p.epilogue = int(g.epilogue), p.out_fp32 = g.out == Dtype::FP32;
+    const int stage_bytes = StageABytes + p.bn * BK * 2;
+    const int staging = 4 * p.slots * SlotBytes;
+    p.stages = (MaxShared - 1024 - ControlBytes - staging) / stage_bytes;
+    if (p.stages > MaxStages)
+        p.stages = MaxStages;
+    const int shared = p.stages * stage_bytes + staging + ControlBytes + 1024;
     p.c = g.c, p.c2 = g.c2, p.r = g.r;
     p.ldc = g.ldc, p.ldr = g.ldr, p.c_batch = g.c_batch, p.r_batch = g.r_batch;
     p.alpha = g.alpha, p.beta = g.beta;
     p.counters = counters;
+    {
+        const int per32 = p.out_fp32 ? 8 : 16; // elements per 32 bytes
+        auto aligned32 = [&](const void *ptr, int64_t ld, int64_t batch_stride) {
+            return !ptr || (reinterpret_cast<uintptr_t>(ptr) % 32 == 0 && ld % per32 == 0 && batch_stride % per32 == 0);
+        };
+        p.wide = aligned32(g.c, g.ldc, g.c_batch) && aligned32(g.c2, g.ldc, g.c_batch) &&
+                 aligned32(g.r, g.ldr, g.r_batch);
+    }
     if (p.splits > 1) {
         size_t bytes = size_t(p.splits) * g.batch * m_tiles * BM * n_tiles * p.bn * sizeof(float);
         Workspace &w = workspace_for(bytes, size_t(tiles), s);
@@ -463,8 +585,41 @@ void launch_gemm_tc(const GemmArgs &g, int sms, StepCounters *counters, cudaStre
                                : make_map_bf16(g.a, g.k, g.m, g.batch, lda, g.a_batch, BK, BM);
     CUtensorMap map_b = p.b_mn ? make_map_bf16(g.b, g.n, g.k, g.batch, ldb, g.b_batch, 64, BK)
                                : make_map_bf16(g.b, g.k, g.n, g.batch, ldb, g.b_batch, BK, p.bn);
+    const int element = p.out_fp32 ? 4 : 2;
+    CUtensorMap map_c = make_map(g.c, element, g.n, g.m, g.batch, g.ldc, g.c_batch, 128 / element, 32);
+    CUtensorMap map_c2 = g.c2 ? make_map(g.c2, element, g.n, g.m, g.batch, g.ldc, g.c_batch, 128 / element, 32) : map_c;
+    CUtensorMap map_r = g.r ? make_map(g.r, element, g.n, g.m, g.batch, g.ldr, g.r_batch, 128 / element, 32) : map_c;
     long long work = tiles * p.splits;
     int grid = int(work < sms ? work : sms);
-    gemm_tc_kernel<<<grid, Threads, SharedBytes, s>>>(map_a, map_b, p);
+    auto launch = [&](auto kernel) {
+        // The opt-in shared-memory size is an attribute of each instantiation on each device.
+        static std::mutex guard;
+        static std::unordered_map<const void *, unsigned long long> configured; // kernel -> device bit mask
+        int device = 0;
+        CHECK_CUDA(cudaGetDevice(&device));
+        {
+            std::lock_guard<std::mutex> lock(guard);
+            unsigned long long &mask = configured[reinterpret_cast<const void *>(kernel)];
+            if (!(mask >> (device & 63) & 1ull)) {
+                CHECK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, MaxShared));
+                mask |= 1ull << (device & 63);
+            }
+        }
+        kernel<<<grid, Threads, shared, s>>>(map_a, map_b, map_c, map_c2, map_r, p);
+    };
+    if (p.out_fp32) {
+        if (g.epilogue == Epilogue::Axpby)
+            launch(gemm_tc_kernel<int(Epilogue::Axpby), true>);
+        else
+            launch(gemm_tc_kernel<int(Epilogue::Store), true>);
+    } else {
+        switch (g.epilogue) {
+        case Epilogue::Store: launch(gemm_tc_kernel<int(Epilogue::Store), false>); break;
+        case Epilogue::Residual: launch(gemm_tc_kernel<int(Epilogue::Residual), false>); break;
+        case Epilogue::GeluDual: launch(gemm_tc_kernel<int(Epilogue::GeluDual), false>); break;
+        case Epilogue::GeluGrad: launch(gemm_tc_kernel<int(Epilogue::GeluGrad), false>); break;
+        case Epilogue::Axpby: launch(gemm_tc_kernel<int(Epilogue::Axpby), false>); break;
+        }
+    }
     CHECK_CUDA(cudaGetLastError());
 }

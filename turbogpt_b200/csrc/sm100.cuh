@@ -30,23 +30,28 @@ inline TensorMapEncoder tensor_map_encoder() {
 // BF16 tensor [batch][outer][inner] with `inner` contiguous, `ld` elements between outer rows and
 // `batch_stride` elements between batches; box [1][box_outer][box_inner]; 128-byte swizzle.
 // Out-of-range box parts are filled with zeros.
-inline CUtensorMap make_map_bf16(const void *base, uint64_t inner, uint64_t outer, uint64_t batch, uint64_t ld,
-                                 uint64_t batch_stride, uint32_t box_inner, uint32_t box_outer) {
-    if (reinterpret_cast<uintptr_t>(base) % 16 || ld % 8 || batch_stride % 8 || box_inner * 2 != 128 ||
-        box_outer > 256)
+// `element` is 2 (BF16) or 4 (FP32) bytes; the box is always 128 bytes wide.
+inline CUtensorMap make_map(const void *base, int element, uint64_t inner, uint64_t outer, uint64_t batch,
+                            uint64_t ld, uint64_t batch_stride, uint32_t box_inner, uint32_t box_outer) {
+    if (reinterpret_cast<uintptr_t>(base) % 16 || (ld * element) % 16 || (batch_stride * element) % 16 ||
+        box_inner * element != 128 || box_outer > 256)
         throw std::runtime_error("tensor map: operand is not 16-byte aligned or the box is out of range");
     CUtensorMap map;
     cuuint64_t dims[3] = {inner, outer, batch};
-    cuuint64_t strides[2] = {ld * 2, (batch > 1 ? batch_stride : ld * outer) * 2};
+    cuuint64_t strides[2] = {ld * element, (batch > 1 ? batch_stride : ld * outer) * element};
     cuuint32_t box[3] = {box_inner, box_outer, 1};
     cuuint32_t element_strides[3] = {1, 1, 1};
-    CUresult r = tensor_map_encoder()(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void *>(base), dims,
-                                      strides, box, element_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                                      CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    CUresult r = tensor_map_encoder()(
+        &map, element == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3,
+        const_cast<void *>(base), dims, strides, box, element_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
+        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS)
         throw std::runtime_error("cuTensorMapEncodeTiled failed with code " + std::to_string(int(r)));
     return map;
+}
+inline CUtensorMap make_map_bf16(const void *base, uint64_t inner, uint64_t outer, uint64_t batch, uint64_t ld,
+                                 uint64_t batch_stride, uint32_t box_inner, uint32_t box_outer) {
+    return make_map(base, 2, inner, outer, batch, ld, batch_stride, box_inner, box_outer);
 }
 
 #ifdef __CUDACC__
@@ -123,6 +128,24 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *map
                  "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y), "r"(z)
                  : "memory");
 }
+// 3-D tile store from shared memory; parts of the box outside the tensor are not written.
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap *map, uint32_t src, int x, int y, int z) {
+    asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(
+                     reinterpret_cast<uint64_t>(map)),
+                 "r"(src), "r"(x), "r"(y), "r"(z)
+                 : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// Waits until at most `pending` of this thread's store groups still read shared memory.
+__device__ __forceinline__ void bulk_wait_read(int pending) {
+    switch (pending) {
+    case 0: asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); break;
+    case 1: asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); break;
+    case 2: asm volatile("cp.async.bulk.wait_group.read 2;" ::: "memory"); break;
+    default: asm volatile("cp.async.bulk.wait_group.read 3;" ::: "memory"); break;
+    }
+}
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 __device__ __forceinline__ void prefetch_map(const CUtensorMap *map) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
 }

@@ -1,0 +1,140 @@
+"""Kernel microbenchmarks through the C ABI (device-resident BF16 inputs N(0,1), seed 0).
+
+    python -m turbogpt_b200.microbench                      # all kernels, one line each
+    python -m turbogpt_b200.microbench --only gemm --iters 20
+    python -m turbogpt_b200.microbench --only gemm --shape 32768,3072,768 --layout kk --iters 3
+
+GEMM shapes are the step's projections at 32 768 tokens: (M,N,K) = (32768,3072,768),
+(32768,768,3072), (32768,2304,768), (32768,768,768), their input-gradient forms (B read
+MN-major) and weight-gradient forms (both operands MN-major, K = 32768).  Attention is causal,
+B=32, H=12, T=1024, d_head=64 (FLOPs counted on the causal half).  Cross-entropy is 256-way over
+[32768, 256] logits.  Times are CUDA-event averages after warm-up; every kernel's operands exceed
+the 126 MB L2 or are rotated over several buffers so that they do.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+
+import torch
+
+from . import bridge
+
+
+def _time(fn, iters: int, warmup: int = 3) -> float:
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(iters):
+        fn()
+    end.record()
+    torch.cuda.synchronize()
+    return start.elapsed_time(end) / iters * 1e-3
+
+
+def gemm_case(lib, m, n, k, layout, iters, out_fp32=False, tensor_cores=True):
+    """layout: two letters, k = K-major, m = MN-major, for A then B."""
+    g = torch.Generator(device="cuda").manual_seed(0)
+    a_mn, b_mn = layout[0] == "m", layout[1] == "m"
+    rotate = max(1, min(4, int(300e6 // ((m * k + n * k) * 2 + m * n * (4 if out_fp32 else 2))) + 1))
+    a = [torch.randn((k, m) if a_mn else (m, k), generator=g, device="cuda").bfloat16() for _ in range(rotate)]
+    b = [torch.randn((k, n) if b_mn else (n, k), generator=g, device="cuda").bfloat16() for _ in range(rotate)]
+    c = [torch.empty(m, n, device="cuda", dtype=torch.float32 if out_fp32 else torch.bfloat16) for _ in range(rotate)]
+    sa = (1, m) if a_mn else (k, 1)
+    sb = (1, n) if b_mn else (k, 1)
+    state = {"i": 0}
+
+    def run():
+        i = state["i"] = (state["i"] + 1) % rotate
+        status = lib.tg_ex_gemm(a[i].data_ptr(), *sa, b[i].data_ptr(), *sb, c[i].data_ptr(), n, m, n, k,
+                                int(out_fp32), int(tensor_cores), None)
+        if status:
+            raise RuntimeError(lib.tg_error().decode())
+
+    seconds = _time(run, iters)
+    return {"kernel": "gemm", "m": m, "n": n, "k": k, "layout": layout, "out": "fp32" if out_fp32 else "bf16",
+            "us": seconds * 1e6, "tflops": 2.0 * m * n * k / seconds / 1e12}
+
+
+def attention_case(lib, batch, context, heads, iters, backward):
+    d_head, width = 64, heads * 64
+    g = torch.Generator(device="cuda").manual_seed(0)
+    qkv = torch.randn(batch * context, 3 * width, generator=g, device="cuda").bfloat16()
+    dout = torch.randn(batch * context, width, generator=g, device="cuda").bfloat16()
+    out = torch.empty(batch * context, width, device="cuda", dtype=torch.bfloat16)
+    lse = torch.empty(batch * heads * context, device="cuda")
+    dqkv = torch.empty_like(qkv)
+    lib.tg_ex_attention_forward(qkv.data_ptr(), out.data_ptr(), lse.data_ptr(), batch, context, heads, d_head, 1, None)
+
+    def forward():
+        if lib.tg_ex_attention_forward(qkv.data_ptr(), out.data_ptr(), lse.data_ptr(), batch, context, heads, d_head,
+                                       1, None):
+            raise RuntimeError(lib.tg_error().decode())
+
+    def back():
+        if lib.tg_ex_attention_backward(qkv.data_ptr(), out.data_ptr(), dout.data_ptr(), lse.data_ptr(),
+                                        dqkv.data_ptr(), batch, context, heads, d_head, 1, None):
+            raise RuntimeError(lib.tg_error().decode())
+
+    seconds = _time(back if backward else forward, iters)
+    flops = 4.0 * batch * heads * context * context * d_head / 2 * (2.5 if backward else 1.0)
+    return {"kernel": "attention_backward" if backward else "attention_forward", "batch": batch, "context": context,
+            "heads": heads, "us": seconds * 1e6, "tflops": flops / seconds / 1e12}
+
+
+def cross_entropy_case(lib, rows, iters):
+    g = torch.Generator(device="cuda").manual_seed(0)
+    rotate = 8  # 8 x 33.6 MB of logits + gradients: beyond L2
+    logits = [torch.randn(rows, 256, generator=g, device="cuda").bfloat16() for _ in range(rotate)]
+    grads = [torch.empty_like(l) for l in logits]
+    targets = torch.randint(0, 256, (rows,), generator=g, device="cuda").to(torch.uint8)
+    losses = torch.empty(rows, device="cuda")
+    state = {"i": 0}
+
+    def run():
+        i = state["i"] = (state["i"] + 1) % rotate
+        if lib.tg_ex_cross_entropy(logits[i].data_ptr(), targets.data_ptr(), losses.data_ptr(), grads[i].data_ptr(),
+                                   rows, 1.0 / rows, None):
+            raise RuntimeError(lib.tg_error().decode())
+
+    seconds = _time(run, iters)
+    bytes_moved = rows * 256 * 2 * 2 + rows * 5
+    return {"kernel": "cross_entropy", "rows": rows, "us": seconds * 1e6, "gbs": bytes_moved / seconds / 1e9}
+
+
+def main() -> None:
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--only", default="all")
+    parser.add_argument("--shape", default="")
+    parser.add_argument("--layout", default="")
+    parser.add_argument("--iters", type=int, default=20)
+    args = parser.parse_args()
+    lib = bridge.load_library()
+    results = []
+    tokens = 32768
+    if args.only in ("all", "gemm"):
+        if args.shape:
+            m, n, k = (int(v) for v in args.shape.split(","))
+            cases = [(m, n, k, args.layout or "kk")]
+        else:
+            cases = []
+            for n, k in [(3072, 768), (768, 3072), (2304, 768), (768, 768)]:
+                cases.append((tokens, n, k, "kk"))   # y = x W^T
+                cases.append((tokens, k, n, "km"))   # dx = dy W
+                cases.append((n, k, tokens, "mm"))   # dW = dy^T x
+        for m, n, k, layout in cases:
+            results.append(gemm_case(lib, m, n, k, layout, args.iters, out_fp32=layout == "mm"))
+    if args.only in ("all", "attention", "attention_forward"):
+        results.append(attention_case(lib, 32, 1024, 12, args.iters, False))
+    if args.only in ("all", "attention", "attention_backward"):
+        results.append(attention_case(lib, 32, 1024, 12, args.iters, True))
+    if args.only in ("all", "cross_entropy"):
+        results.append(cross_entropy_case(lib, tokens, args.iters))
+    for r in results:
+        print(json.dumps(r))
+
+
+if __name__ == "__main__":
+    main()
