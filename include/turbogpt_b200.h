@@ -144,6 +144,18 @@ int64_t tg_ex_launch_count(Engine *engine);
  * cuda/mma.cuh:77-108 and cuda/ops.cuh:30-55,83-109.  out_fp32: C is float, else BF16. */
 int tg_ex_gemm(const void *a, int64_t a_row, int64_t a_col, const void *b, int64_t b_row, int64_t b_col,
                void *c, int64_t ldc, int m, int n, int k, int out_fp32, int tensor_cores, void *stream);
+/* No counterpart in the reference (its engine allocates everything in tg_create).  Weight gradient
+ * dw[out, in] (FP32) = dy[tokens, out]^T x[tokens, in] (BF16, row-major, device pointers) for callers
+ * that must not allocate device memory when they need it — a process whose memory pool already owns
+ * the whole GPU, or a loop that cannot afford the allocator's device-wide synchronisation.  The
+ * split-K scratch is a 16 MiB array built into the library (every GPU that loads the library holds it
+ * until exit): shapes needing more, or more than 1024 output tiles, are refused with a message; no
+ * cudaMalloc/cudaFree or allocating library call is made.  The first call on a device looks up the
+ * array's device address (cudaGetSymbolAddress) and should come before any stream capture.  All calls
+ * share the array, which keeps the previous call's contents (the part that must start at zero is
+ * cleared on `stream` first): calls that overlap on the GPU race.  Results equal tg_ex_gemm's. */
+int tg_ex_weight_gradient_static(const void *dy, const void *x, float *dw, int out, int in, int tokens,
+                                 void *stream);
 /* Causal softmax attention over packed qkv [batch*context, 3*heads*d_head] (q | k | v);
  * out [batch*context, heads*d_head]; lse [batch, heads, context] floats. */
 int tg_ex_attention_forward(const void *qkv, void *out, float *lse, int batch, int context, int heads,

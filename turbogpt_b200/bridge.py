@@ -133,6 +133,7 @@ def load_library() -> C.CDLL:
     lib.tg_ex_launch_count.argtypes = [P]
     lib.tg_ex_launch_count.restype = I64
     lib.tg_ex_gemm.argtypes = [P, I64, I64, P, I64, I64, P, I64, I, I, I, I, I, P]
+    lib.tg_ex_weight_gradient_static.argtypes = [P, P, P, I, I, I, P]
     lib.tg_ex_attention_forward.argtypes = [P, P, P, I, I, I, I, I, P]
     lib.tg_ex_attention_backward.argtypes = [P, P, P, P, P, I, I, I, I, I, P]
     lib.tg_ex_cross_entropy.argtypes = [P, P, P, P, I, C.c_float, P]
@@ -144,7 +145,7 @@ EXPORTS = ('error create destroy parameter_count blocks shared_bytes set_weights
            'set_optimizer_state memory set_data train get_training_losses training_versions pipeline_stats '
            'onecycle_point set_onecycle batch predict optimizer_test synchronize').split()
 EXTENSIONS = ('reference_config gpt_config parameter_count parameter_layout initialize_weights nccl_unique_id '
-              'stream sample train_mean_loss train_batch profile launch_count gemm attention_forward attention_backward '
+              'stream sample train_mean_loss train_batch profile launch_count gemm weight_gradient_static attention_forward attention_backward '
               'cross_entropy').split()
 
 

@@ -623,3 +623,97 @@ void launch_gemm_tc(const GemmArgs &g, int sms, StepCounters *counters, cudaStre
     }
     CHECK_CUDA(cudaGetLastError());
 }
+
+// ------------------------------------------------------------------------------------------
+// Weight gradient without any allocation.  Some hosts may not call cudaMalloc at the moment they
+// need a gradient: a serving or training process that has handed the whole device to its own
+// memory pool, a caller inside a region where the allocator's implicit device synchronisation is
+// not acceptable, or one whose memory budget was fixed when the process started.  For them the
+// split-K scratch (FP32 partial tiles and the per-tile tickets) lives in the array below, which
+// every GPU that loads this library holds until the process exits.
+//
+// In host code `static_scratch` is only a stand-in for the symbol: its device address comes from
+// cudaGetSymbolAddress, fetched once per device with that device current, on the first call for
+// that device (so the first call should happen before any stream capture).  All calls share the
+// array and it keeps the previous call's contents: the tickets are cleared on the stream before
+// every launch, the partial tiles are fully overwritten before they are read.  Two calls that
+// overlap on the GPU (different streams, or different threads) race on it.
+// ------------------------------------------------------------------------------------------
+namespace {
+constexpr size_t StaticPartialBytes = size_t(16) << 20; // 16 MiB of FP32 partial tiles
+constexpr int StaticTickets = 1024;                      // output tiles
+static __device__ __align__(256) unsigned char static_scratch[StaticPartialBytes + StaticTickets * sizeof(unsigned)];
+void *static_scratch_address[64] = {}; // per device, filled on first use
+} // namespace
+
+size_t gemm_tc_static_scratch_bytes() { return StaticPartialBytes; }
+
+void launch_weight_gradient_static(const void *dy, const void *x, float *dw, int out, int in, int tokens,
+                                   int sms, cudaStream_t s) {
+    // dW[out, in] = dy[tokens, out]^T x[tokens, in]: both operands MN-major, K = tokens.
+    GemmArgs g;
+    g.in = Dtype::BF16, g.out = Dtype::FP32;
+    g.a = dy, g.a_row = 1, g.a_col = out, g.b = x, g.b_row = 1, g.b_col = in;
+    g.c = dw, g.ldc = in, g.m = out, g.n = in, g.k = tokens;
+    if (!gemm_tc_supported(g))
+        throw std::runtime_error("weight gradient: sizes must be multiples of 8 (out, in), at least 64, and the "
+                                 "pointers 16-byte aligned");
+    int device = 0;
+    CHECK_CUDA(cudaGetDevice(&device));
+    if (device < 0 || device >= 64)
+        throw std::runtime_error("weight gradient: device index out of range");
+    auto kernel = gemm_tc_kernel<int(Epilogue::Store), true>;
+    if (!static_scratch_address[device]) { // set-up, once per device, with that device current
+        void *address = nullptr;
+        CHECK_CUDA(cudaGetSymbolAddress(&address, static_scratch));
+        CHECK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, MaxShared));
+        static_scratch_address[device] = address;
+    }
+    TcParams p{};
+    p.m = g.m, p.n = g.n, p.k = g.k, p.batch = 1;
+    p.a_mn = 1, p.b_mn = 1, p.epilogue = int(Epilogue::Store), p.out_fp32 = 1;
+    const int m_tiles = (g.m + BM - 1) / BM, k_blocks = (g.k + BK - 1) / BK;
+    long long best_time = 0;
+    for (int bn : {256, 192, 128, 64}) { // same cost model as launch_gemm_tc
+        if (bn > 64 && bn - 64 >= g.n)
+            continue;
+        const long long tiles = (long long)m_tiles * ((g.n + bn - 1) / bn);
+        const int block_cost = bn / 2 > (128 + bn) / 4 ? bn / 2 : (128 + bn) / 4;
+        for (int splits : {1, 2, 3, 4, 6, 8, 12, 16}) {
+            if (splits > 1 && (k_blocks / splits < 8 || tiles * splits > sms))
+                continue;
+            const int per = (k_blocks + splits - 1) / splits;
+            if (splits > 1 && (k_blocks + per - 1) / per != splits)
+                continue;
+            const long long rounds = (tiles * splits + sms - 1) / sms;
+            const long long time = rounds * ((long long)per * (block_cost + 16) + bn + (splits > 1 ? splits * bn / 2 : 0));
+            if (!p.bn || time < best_time)
+                p.bn = bn, p.splits = splits, p.k_blocks_per_split = per, best_time = time;
+        }
+    }
+    const int n_tiles = (g.n + p.bn - 1) / p.bn;
+    const long long tiles = (long long)m_tiles * n_tiles;
+    const size_t needed = p.splits > 1 ? size_t(p.splits) * m_tiles * BM * n_tiles * p.bn * sizeof(float) : 0;
+    if (needed > StaticPartialBytes || (p.splits > 1 && tiles > StaticTickets))
+        throw std::runtime_error("weight gradient: this shape needs " + std::to_string(needed) + " bytes of scratch in " +
+                                 std::to_string(tiles) + " tiles; the built-in array holds " +
+                                 std::to_string(StaticPartialBytes) + " bytes and " + std::to_string(StaticTickets) +
+                                 " tiles (use tg_ex_gemm, which allocates)");
+    const int stage_bytes = StageABytes + p.bn * BK * 2;
+    p.stages = (MaxShared - 1024 - ControlBytes) / stage_bytes;
+    if (p.stages > MaxStages)
+        p.stages = MaxStages;
+    const int shared = p.stages * stage_bytes + ControlBytes + 1024;
+    p.c = g.c, p.ldc = g.ldc, p.alpha = 1.f, p.beta = 0.f;
+    p.wide = reinterpret_cast<uintptr_t>(g.c) % 32 == 0 && g.ldc % 8 == 0;
+    unsigned char *scratch = static_cast<unsigned char *>(static_scratch_address[device]);
+    p.workspace = reinterpret_cast<float *>(scratch);
+    p.tickets = reinterpret_cast<unsigned *>(scratch + StaticPartialBytes);
+    CHECK_CUDA(cudaMemsetAsync(p.tickets, 0, StaticTickets * sizeof(unsigned), s)); // must start at zero
+    CUtensorMap map_a = make_map_bf16(g.a, g.m, g.k, 1, g.a_col, 0, 64, BK);
+    CUtensorMap map_b = make_map_bf16(g.b, g.n, g.k, 1, g.b_col, 0, 64, BK);
+    CUtensorMap map_c = make_map(g.c, 4, g.n, g.m, 1, g.ldc, 0, 32, 32);
+    const long long work = tiles * p.splits;
+    kernel<<<int(work < sms ? work : sms), Threads, shared, s>>>(map_a, map_b, map_c, map_c, map_c, p);
+    CHECK_CUDA(cudaGetLastError());
+}

@@ -166,6 +166,11 @@ void launch_gemm_simt(const GemmArgs &g, cudaStream_t s);
 bool gemm_tc_supported(const GemmArgs &g);
 void launch_gemm_tc(const GemmArgs &g, int sms, StepCounters *counters, cudaStream_t s);
 int gemm_tc_shared_bytes();
+// Weight gradient dW[out, in] = dy^T x whose split-K scratch is a fixed array inside the library:
+// allocates nothing (see gemm_tc.cu).  Throws when the shape needs more scratch than the array holds.
+void launch_weight_gradient_static(const void *dy, const void *x, float *dw, int out, int in, int tokens, int sms,
+                                   cudaStream_t s);
+size_t gemm_tc_static_scratch_bytes();
 
 // ---- optimizer (reference cuda/optim.cuh) ----
 void launch_sum_squares(const float *gradient, int64_t count, float *partial, int blocks, cudaStream_t s);

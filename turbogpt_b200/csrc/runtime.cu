@@ -254,6 +254,15 @@ int tg_ex_gemm(const void *a, int64_t a_row, int64_t a_col, const void *b, int64
         CHECK_CUDA(cudaGetLastError());
     });
 }
+int tg_ex_weight_gradient_static(const void *dy, const void *x, float *dw, int out, int in, int tokens,
+                                 void *stream) {
+    return guarded([&] {
+        require_sm100();
+        if (!dy || !x || !dw)
+            throw std::runtime_error("Missing weight-gradient operand");
+        launch_weight_gradient_static(dy, x, dw, out, in, tokens, device_sms(), static_cast<cudaStream_t>(stream));
+    });
+}
 int tg_ex_attention_forward(const void *qkv, void *out, float *lse, int batch, int context, int heads, int d_head,
                             int tensor_cores, void *stream) {
     return guarded([&] {
