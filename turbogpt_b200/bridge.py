@@ -81,6 +81,34 @@ def library_path() -> Path:
 _library = None
 
 
+def declare_reference_interface(lib: C.CDLL) -> C.CDLL:
+    """ctypes signatures of the 22 functions of the reference's runtime.h on any library that
+    exports them (this one, or the reference's own engine)."""
+    P, I, I64 = C.c_void_p, C.c_int, C.c_int64
+    lib.tg_error.restype = C.c_char_p
+    lib.tg_create.argtypes = [C.POINTER(Config)]
+    lib.tg_create.restype = P
+    lib.tg_destroy.restype = None
+    for name in ('destroy', 'parameter_count', 'blocks', 'shared_bytes', 'synchronize'):
+        getattr(lib, 'tg_' + name).argtypes = [P]
+    for name in ('set_weights', 'get_weights'):
+        getattr(lib, 'tg_' + name).argtypes = [P, P]
+    lib.tg_get_optimizer_state.argtypes = [P, P, P, C.POINTER(C.c_uint64)]
+    lib.tg_set_optimizer_state.argtypes = [P, P, P, C.c_uint64]
+    lib.tg_memory.argtypes = [P, C.POINTER(C.c_double)]
+    lib.tg_set_data.argtypes = [P, P, I64]
+    lib.tg_train.argtypes = [P, I]
+    lib.tg_get_training_losses.argtypes = [P, P, I]
+    lib.tg_training_versions.argtypes = [P, P, I]
+    lib.tg_pipeline_stats.argtypes = [P, C.POINTER(C.c_double), C.POINTER(C.c_int)]
+    lib.tg_batch.argtypes = [P] * 6
+    lib.tg_predict.argtypes = [P, P, P]
+    lib.tg_optimizer_test.argtypes = [P, P, I]
+    lib.tg_set_onecycle.argtypes = [P, C.POINTER(OneCycle)]
+    lib.tg_onecycle_point.argtypes = [C.POINTER(OneCycle), I, C.POINTER(StepRates)]
+    return lib
+
+
 def load_library() -> C.CDLL:
     """Loads the CUDA library and declares every export.  Raises if it is missing: there is
     no fallback implementation."""
@@ -153,8 +181,8 @@ class Native:
     """An engine.  ``Native(Config(...))`` is the reference architecture exactly as
     tests/bridge.py's Native; ``Native(ConfigEx...)`` any architecture."""
 
-    def __init__(self, config):
-        self.lib = lib = load_library()
+    def __init__(self, config, library=None):
+        self.lib = lib = library or load_library()
         if isinstance(config, ConfigEx):
             self.extended, self.config = config, config.base
             self.handle = lib.tg_create_ex(C.byref(config))

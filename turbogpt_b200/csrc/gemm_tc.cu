@@ -22,7 +22,9 @@
 // atomic ticket, no spinning) sums the partials in split order, so results are deterministic.
 #include "device_utils.cuh"
 #include "sm100.cuh"
+#include <cstdlib>
 #include <mutex>
+#include <type_traits>
 #include <unordered_map>
 
 using namespace sm100;
@@ -150,7 +152,11 @@ __device__ __forceinline__ void unpack8(uint4 u, float (&v)[8]) {
     }
 }
 
-template <int Kind, bool OutFp32>
+// Pair = true: the CTA is half of a cluster of two that computes a 256-row tile with
+// cta_group::2 MMAs issued by the pair's first CTA.  Each CTA stages its own 128 rows of A and half
+// of the B tile (the tensor core reads the other half from the partner's shared memory), so a
+// K block costs each SM 16 KB + BN/2 x 128 B instead of 16 KB + BN x 128 B and the ring is deeper.
+template <int Kind, bool OutFp32, bool Pair>
 __global__ void __launch_bounds__(Threads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                const __grid_constant__ CUtensorMap map_c, const __grid_constant__ CUtensorMap map_c2,
@@ -158,7 +164,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     extern __shared__ uint8_t raw_shared[];
     const uint32_t base = (smem_address(raw_shared) + 1023u) & ~1023u;
     uint8_t *aligned = raw_shared + (base - smem_address(raw_shared));
-    const int stage_bytes = StageABytes + p.bn * BK * 2;
+    constexpr int Unit = Pair ? 2 : 1;
+    const uint32_t rank = Pair ? cluster_rank() : 0u;
+    const int bn_local = p.bn / Unit; // B rows staged by this CTA
+    const int stage_bytes = StageABytes + bn_local * BK * 2;
     uint64_t *barriers = reinterpret_cast<uint64_t *>(aligned + p.stages * stage_bytes + 4 * p.slots * SlotBytes);
     // barrier slots: full[8], empty[8], tmem_full[2], tmem_empty[2], r_full[4 warps][4 slots]
     const uint32_t full0 = smem_address(barriers), empty0 = full0 + 8 * MaxStages, tfull0 = empty0 + 8 * MaxStages,
@@ -175,7 +184,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         }
         for (int b = 0; b < 2; ++b) {
             mbarrier_init(tfull0 + 8 * b, 1);
-            mbarrier_init(tempty0 + 8 * b, EpilogueWarps);
+            mbarrier_init(tempty0 + 8 * b, EpilogueWarps * Unit);
         }
         for (int i = 0; i < 16; ++i)
             mbarrier_init(rfull0 + 8 * i, 1);
@@ -186,28 +195,39 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         prefetch_map(&map_c);
     }
     if (warp == 1) {
-        tmem_alloc(smem_address(tmem_slot), TmemColumns);
-        tmem_relinquish();
+        if constexpr (Pair) {
+            tmem_alloc_pair(smem_address(tmem_slot), TmemColumns);
+            tmem_relinquish_pair();
+        } else {
+            tmem_alloc(smem_address(tmem_slot), TmemColumns);
+            tmem_relinquish();
+        }
     }
     tcgen05_fence_before();
     __syncthreads();
+    if constexpr (Pair)
+        cluster_sync_all(); // the partner's barriers exist before anything signals them
     tcgen05_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
-    const int m_tiles = (p.m + BM - 1) / BM, n_tiles = (p.n + p.bn - 1) / p.bn;
+    // Tiles along M are scheduled per CTA pair; m_tiles counts 128-row tiles including padding.
+    const int m_tiles = ((p.m + BM * Unit - 1) / (BM * Unit)) * Unit, n_tiles = (p.n + p.bn - 1) / p.bn;
     const int k_blocks = (p.k + BK - 1) / BK;
-    const long long work_items = (long long)m_tiles * n_tiles * p.batch * p.splits;
-    const uint32_t stage_tx = stage_bytes;
+    const int m_units = m_tiles / Unit;
+    const long long work_items = (long long)m_units * n_tiles * p.batch * p.splits;
+    const long long first_item = blockIdx.x / Unit, item_stride = gridDim.x / Unit;
+    const uint32_t stage_tx = stage_bytes * Unit; // bytes landing for one stage in both CTAs
 
     if (warp == 0) {
         // ---------------- TMA producer ----------------
         if (elect_one()) {
             int stage = 0;
             uint32_t phase = 0;
-            for (long long w = blockIdx.x; w < work_items; w += gridDim.x) {
+            for (long long w = first_item; w < work_items; w += item_stride) {
                 const int split = int(w % p.splits);
                 long long t = w / p.splits;
-                const int nt = int(t % n_tiles), mt = int(t / n_tiles % m_tiles), z = int(t / n_tiles / m_tiles);
+                const int nt = int(t % n_tiles), mt = int(t / n_tiles % m_units) * Unit + int(rank),
+                      z = int(t / n_tiles / m_units);
                 const int kb0 = split * p.k_blocks_per_split;
                 const int kb1 = min(k_blocks, kb0 + p.k_blocks_per_split);
                 bool ok = true;
@@ -215,19 +235,29 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     ok = mbarrier_wait(empty0 + 8 * stage, phase ^ 1, abort_flag, p.counters, 101);
                     if (!ok)
                         break;
-                    const uint32_t bar = full0 + 8 * stage, sa = base + stage * stage_bytes, sb = sa + StageABytes;
-                    mbarrier_expect_tx(bar, stage_tx);
+                    const uint32_t sa = base + stage * stage_bytes, sb = sa + StageABytes;
+                    // Both CTAs' bytes are counted on the first CTA's barrier, armed by that CTA.
+                    const uint32_t bar = Pair ? cluster_address(full0 + 8 * stage, 0) : full0 + 8 * stage;
+                    if (rank == 0)
+                        mbarrier_expect_tx(full0 + 8 * stage, stage_tx);
+                    auto load = [&](uint32_t dst, const CUtensorMap *map, int x, int y) {
+                        if constexpr (Pair)
+                            tma_load_3d_pair(dst, map, x, y, z, bar);
+                        else
+                            tma_load_3d(dst, map, x, y, z, bar);
+                    };
+                    const int n_first = nt * p.bn + int(rank) * bn_local;
                     if (!p.a_mn) {
-                        tma_load_3d(sa, &map_a, kb * BK, mt * BM, z, bar);
+                        load(sa, &map_a, kb * BK, mt * BM);
                     } else {
                         for (int j = 0; j < BM / 64; ++j)
-                            tma_load_3d(sa + j * 64 * BK * 2, &map_a, mt * BM + j * 64, kb * BK, z, bar);
+                            load(sa + j * 64 * BK * 2, &map_a, mt * BM + j * 64, kb * BK);
                     }
                     if (!p.b_mn) {
-                        tma_load_3d(sb, &map_b, kb * BK, nt * p.bn, z, bar);
+                        load(sb, &map_b, kb * BK, n_first);
                     } else {
-                        for (int j = 0; j < p.bn / 64; ++j)
-                            tma_load_3d(sb + j * 64 * BK * 2, &map_b, nt * p.bn + j * 64, kb * BK, z, bar);
+                        for (int j = 0; j < bn_local / 64; ++j)
+                            load(sb + j * 64 * BK * 2, &map_b, n_first + j * 64, kb * BK);
                     }
                     if (++stage == p.stages) {
                         stage = 0;
@@ -240,15 +270,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         }
     } else if (warp == 1) {
         // ---------------- MMA issuer ----------------
-        if (elect_one()) {
-            const uint32_t instruction = instruction_descriptor(BM, p.bn, p.a_mn, p.b_mn);
+        if (rank == 0 && elect_one()) {
+            const uint32_t instruction = instruction_descriptor(BM * Unit, p.bn, p.a_mn, p.b_mn);
             // Per 16-element K step inside a stage: 32 bytes along a K-major row, or 16 rows of
             // 128 bytes for an MN-major operand.
             const uint32_t a_step = p.a_mn ? 16 * 128 : 32, b_step = p.b_mn ? 16 * 128 : 32;
             const uint32_t a_lbo = p.a_mn ? 64 * BK * 2 : 16, b_lbo = p.b_mn ? 64 * BK * 2 : 16;
             int stage = 0, buffer = 0;
             uint32_t phase = 0, buffer_phase = 0;
-            for (long long w = blockIdx.x; w < work_items; w += gridDim.x) {
+            for (long long w = first_item; w < work_items; w += item_stride) {
                 const int split = int(w % p.splits);
                 const int kb0 = split * p.k_blocks_per_split;
                 const int kb1 = min(k_blocks, kb0 + p.k_blocks_per_split);
@@ -267,9 +297,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     for (int ks = 0; ks < BK / 16; ++ks) {
                         uint64_t da = smem_descriptor(sa + ks * a_step, a_lbo, 1024);
                         uint64_t db = smem_descriptor(sb + ks * b_step, b_lbo, 1024);
-                        tcgen05_mma_bf16(accumulator, da, db, instruction, (kb > kb0 || ks > 0) ? 1u : 0u);
+                        if constexpr (Pair)
+                            tcgen05_mma_bf16_pair(accumulator, da, db, instruction, (kb > kb0 || ks > 0) ? 1u : 0u);
+                        else
+                            tcgen05_mma_bf16(accumulator, da, db, instruction, (kb > kb0 || ks > 0) ? 1u : 0u);
                     }
-                    tcgen05_commit(empty0 + 8 * stage); // frees the stage once these MMAs have read it
+                    // frees the stage (in both CTAs) once these MMAs have read it
+                    if constexpr (Pair) {
+                        tcgen05_commit_pair(cluster_address(empty0 + 8 * stage, 0));
+                        tcgen05_commit_pair(cluster_address(empty0 + 8 * stage, 1));
+                    } else {
+                        tcgen05_commit(empty0 + 8 * stage);
+                    }
                     if (++stage == p.stages) {
                         stage = 0;
                         phase ^= 1;
@@ -277,7 +316,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 }
                 if (!ok)
                     break;
-                tcgen05_commit(tfull0 + 8 * buffer); // accumulator complete
+                if constexpr (Pair) { // accumulator complete, in both CTAs' tensor memory
+                    tcgen05_commit_pair(cluster_address(tfull0 + 8 * buffer, 0));
+                    tcgen05_commit_pair(cluster_address(tfull0 + 8 * buffer, 1));
+                } else {
+                    tcgen05_commit(tfull0 + 8 * buffer);
+                }
                 if (++buffer == 2) {
                     buffer = 0;
                     buffer_phase ^= 1;
@@ -294,10 +338,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                                Kind == int(Epilogue::Axpby);
         int buffer = 0;
         uint32_t buffer_phase = 0;
-        for (long long w = blockIdx.x; w < work_items; w += gridDim.x) {
+        for (long long w = first_item; w < work_items; w += item_stride) {
             const int split = int(w % p.splits);
             long long t = w / p.splits;
-            const int nt = int(t % n_tiles), mt = int(t / n_tiles % m_tiles), z = int(t / n_tiles / m_tiles);
+            const int nt = int(t % n_tiles), mt = int(t / n_tiles % m_units) * Unit + int(rank),
+                      z = int(t / n_tiles / m_units);
             bool ready = mbarrier_wait(tfull0 + 8 * buffer, buffer_phase, abort_flag, p.counters, 104);
             if (p.splits > 1) // the eight warps meet at named barriers below: leave together or not at all
                 ready = epilogue_all(ready);
@@ -392,55 +437,74 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 }
                 tcgen05_fence_before();
                 __syncwarp();
-                if (lane == 0)
-                    mbarrier_arrive(tempty0 + 8 * buffer);
+                if (lane == 0) {
+                    if constexpr (Pair)
+                        mbarrier_arrive_cluster(cluster_address(tempty0 + 8 * buffer, 0));
+                    else
+                        mbarrier_arrive(tempty0 + 8 * buffer);
+                }
             } else {
-                // Partial tile to the workspace (padded to whole tiles, so no bounds checks).
+                // Partial tile to the workspace (padded to whole tiles, so no bounds checks).  A 32 x 32
+                // chunk is stored column by column (lane = row), so every access is one 128-byte line.
                 const long long padded_m = (long long)m_tiles * BM, padded_n = (long long)n_tiles * p.bn;
+                const long long split_stride = (long long)p.batch * padded_m * padded_n;
                 float *partial = p.workspace + ((long long)split * p.batch + z) * padded_m * padded_n;
+                const long long chunk_row = ((long long)mt * 4 + quarter) * (padded_n / 32) + nt * (p.bn / 32);
                 for (int chunk = share; chunk < p.bn / 32; chunk += Shares) {
                     float v[32];
                     tmem_load_32x32(taddr + chunk * 32, v);
-                    float *out = partial + row * padded_n + nt * p.bn + chunk * 32;
+                    float *out = partial + (chunk_row + chunk) * 1024 + lane;
 #pragma unroll
-                    for (int g = 0; g < 8; ++g)
-                        *reinterpret_cast<float4 *>(out + g * 4) =
-                            make_float4(v[g * 4], v[g * 4 + 1], v[g * 4 + 2], v[g * 4 + 3]);
+                    for (int j = 0; j < 32; ++j)
+                        out[j * 32] = v[j];
                 }
                 tcgen05_fence_before();
                 __syncwarp();
-                if (lane == 0)
-                    mbarrier_arrive(tempty0 + 8 * buffer);
+                if (lane == 0) {
+                    if constexpr (Pair)
+                        mbarrier_arrive_cluster(cluster_address(tempty0 + 8 * buffer, 0));
+                    else
+                        mbarrier_arrive(tempty0 + 8 * buffer);
+                }
                 // Ticket: the split that arrives last reduces the tile in split order.
                 __threadfence();
                 asm volatile("bar.sync 1, 512;" ::: "memory");
                 if (threadIdx.x == 64) {
-                    unsigned ticket = atomicAdd(&p.tickets[t], 1u);
+                    unsigned ticket = atomicAdd(&p.tickets[t * Unit + rank], 1u);
                     int last = ticket == unsigned(p.splits - 1);
                     if (last)
-                        p.tickets[t] = 0; // ready for the next launch
+                        p.tickets[t * Unit + rank] = 0; // ready for the next launch
                     last_split_flag[0] = last;
                 }
                 asm volatile("bar.sync 1, 512;" ::: "memory");
                 if (last_split_flag[0]) {
                     __threadfence();
-                    if (row < p.m) {
-                        for (int col = share * 32; col < p.bn; col += 32 * Shares) {
-                            for (int sub = 0; sub < 32; sub += 8) {
-                                const int c = nt * p.bn + col + sub;
-                                if (c >= p.n)
+                    for (int chunk = share; chunk < p.bn / 32; chunk += Shares) {
+                        const int column = nt * p.bn + chunk * 32;
+                        if (column >= p.n)
+                            break;
+                        // L2 only (__ldcg): the partials were written by other SMs.
+                        const float *src = p.workspace + ((long long)z * padded_m * padded_n) +
+                                           (chunk_row + chunk) * 1024 + lane;
+                        float sum[32];
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            sum[j] = 0.f;
+                        for (int sp = 0; sp < p.splits; ++sp) {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j)
+                                sum[j] += __ldcg(src + sp * split_stride + j * 32);
+                        }
+                        if (row < p.m) {
+#pragma unroll
+                            for (int g = 0; g < 4; ++g) {
+                                if (column + g * 8 >= p.n)
                                     break;
-                                float sum[8] = {};
-                                for (int s = 0; s < p.splits; ++s) {
-                                    // L2 only: the partials were written by other SMs.
-                                    const float4 *src = reinterpret_cast<const float4 *>(
-                                        p.workspace + ((long long)s * p.batch + z) * padded_m * padded_n +
-                                        row * padded_n + c);
-                                    float4 lo = __ldcg(src), hi = __ldcg(src + 1);
-                                    sum[0] += lo.x, sum[1] += lo.y, sum[2] += lo.z, sum[3] += lo.w;
-                                    sum[4] += hi.x, sum[5] += hi.y, sum[6] += hi.z, sum[7] += hi.w;
-                                }
-                                store_group(p, sum, row, c, z);
+                                float group[8];
+#pragma unroll
+                                for (int j = 0; j < 8; ++j)
+                                    group[j] = sum[g * 8 + j];
+                                store_group(p, group, row, column + g * 8, z);
                             }
                         }
                     }
@@ -461,8 +525,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         __nanosleep(2000000);
     tcgen05_fence_before();
     __syncthreads();
-    if (warp == 1)
-        tmem_dealloc(tmem_base, TmemColumns);
+    if constexpr (Pair) {
+        cluster_sync_all(); // neither CTA's tensor or shared memory is released while the other may touch it
+        if (warp == 1)
+            tmem_dealloc_pair(tmem_base, TmemColumns);
+    } else {
+        if (warp == 1)
+            tmem_dealloc(tmem_base, TmemColumns);
+    }
 }
 
 struct Workspace {
@@ -536,33 +606,53 @@ void launch_gemm_tc(const GemmArgs &g, int sms, StepCounters *counters, cudaStre
     // Tile width and K splits by a small cost model, in clocks per 64-deep K block: the MMA
     // takes bn/2, the shared-memory operand reads (128+bn)/4; a tile adds a fixed drain cost and
     // every split one pass over the FP32 partial tile.  Four staging slots leave room for 192 columns.
+    // CTA pairs (256-row tiles) are tried first: they halve the B bytes each SM stages per K block.
+    // TURBOGPT_GEMM_PAIR=0 / 1 forces one form (for measurements).
+    static const int forced_pair = [] {
+        const char *v = getenv("TURBOGPT_GEMM_PAIR");
+        return v ? atoi(v) : -1;
+    }();
     long long best_time = 0;
     p.bn = 0;
-    for (int bn : {256, 192, 128, 64}) {
-        if (bn > 64 && bn - 64 >= g.n)
-            continue; // a narrower tile already covers N
-        const long long tiles = (long long)m_tiles * ((g.n + bn - 1) / bn) * g.batch;
-        const int block_cost = bn / 2 > (128 + bn) / 4 ? bn / 2 : (128 + bn) / 4;
-        for (int splits : {1, 2, 3, 4, 6, 8, 12, 16}) {
-            if (splits > 1 && (k_blocks / splits < 8 || tiles * splits > sms || second_tensor))
-                continue;
-            const int per = (k_blocks + splits - 1) / splits;
-            if (splits > 1 && (k_blocks + per - 1) / per != splits)
-                continue; // would leave an empty split
-            const long long rounds = (tiles * splits + sms - 1) / sms;
-            const long long time = rounds * ((long long)per * (block_cost + 16) + bn + (splits > 1 ? splits * bn / 2 : 0));
-            if (!p.bn || time < best_time)
-                p.bn = bn, p.splits = splits, p.k_blocks_per_split = per, best_time = time;
+    int pair = 0;
+    for (int unit : {2, 1}) {
+        if ((unit == 2 && (forced_pair == 0 || m_tiles < 2 || sms < 2)) || (unit == 1 && forced_pair == 1 && p.bn))
+            continue;
+        const int slots = sms / unit;
+        const long long m_units = (m_tiles + unit - 1) / unit;
+        for (int bn : {256, 192, 128, 64}) {
+            if (bn > 64 && bn - 64 >= g.n)
+                continue; // a narrower tile already covers N
+            if (unit == 2 && (bn == 64 || (p.b_mn && bn == 192)))
+                continue; // each CTA stages bn/2 rows of B: whole 64-row blocks when B is MN-major
+            const long long tiles = m_units * ((g.n + bn - 1) / bn) * g.batch;
+            // Clocks per K block and CTA: the MMA takes bn/2; a single CTA cannot keep its ring full
+            // (measured ~65 % of that rate), a pair can.
+            const int mma = bn / 2 > (128 + bn) / 4 ? bn / 2 : (128 + bn) / 4;
+            const int block_cost = unit == 2 ? mma + 16 : mma * (k_blocks >= 64 ? 9 : 11) / 8 + 16;
+            for (int splits : {1, 2, 3, 4, 6, 8, 12, 16}) {
+                if (splits > 1 && (k_blocks / splits < 8 || tiles * splits > slots || second_tensor))
+                    continue;
+                const int per = (k_blocks + splits - 1) / splits;
+                if (splits > 1 && (k_blocks + per - 1) / per != splits)
+                    continue; // would leave an empty split
+                const long long rounds = (tiles * splits + slots - 1) / slots;
+                const long long time = rounds * ((long long)per * block_cost + bn + (splits > 1 ? splits * bn / 2 : 0));
+                if (!p.bn || time < best_time)
+                    p.bn = bn, p.splits = splits, p.k_blocks_per_split = per, best_time = time, pair = unit == 2;
+            }
         }
     }
+    const int unit = pair ? 2 : 1;
+    const int padded_m_tiles = (m_tiles + unit - 1) / unit * unit;
     const int n_tiles = (g.n + p.bn - 1) / p.bn;
-    const long long tiles = (long long)m_tiles * n_tiles * g.batch;
-    const int stage_bytes = StageABytes + p.bn * BK * 2;
-    const int staging = 4 * p.slots * SlotBytes;
-    p.stages = (MaxShared - 1024 - ControlBytes - staging) / stage_bytes;
+    const long long tiles = (long long)(padded_m_tiles / unit) * n_tiles * g.batch; // scheduling units
+    const int bn_local = p.bn / unit;
+    const int stage_bytes = StageABytes + bn_local * BK * 2;
+    p.stages = (MaxShared - 1024 - ControlBytes) / stage_bytes;
     if (p.stages > MaxStages)
         p.stages = MaxStages;
-    const int shared = p.stages * stage_bytes + staging + ControlBytes + 1024;
+    const int shared = p.stages * stage_bytes + ControlBytes + 1024;
     p.c = g.c, p.c2 = g.c2, p.r = g.r;
     p.ldc = g.ldc, p.ldr = g.ldr, p.c_batch = g.c_batch, p.r_batch = g.r_batch;
     p.alpha = g.alpha, p.beta = g.beta;
@@ -576,21 +666,20 @@ void launch_gemm_tc(const GemmArgs &g, int sms, StepCounters *counters, cudaStre
                  aligned32(g.r, g.ldr, g.r_batch);
     }
     if (p.splits > 1) {
-        size_t bytes = size_t(p.splits) * g.batch * m_tiles * BM * n_tiles * p.bn * sizeof(float);
-        Workspace &w = workspace_for(bytes, size_t(tiles), s);
+        size_t bytes = size_t(p.splits) * g.batch * padded_m_tiles * BM * n_tiles * p.bn * sizeof(float);
+        Workspace &w = workspace_for(bytes, size_t(tiles) * unit, s);
         p.workspace = w.partials;
         p.tickets = w.tickets;
     }
     CUtensorMap map_a = p.a_mn ? make_map_bf16(g.a, g.m, g.k, g.batch, lda, g.a_batch, 64, BK)
                                : make_map_bf16(g.a, g.k, g.m, g.batch, lda, g.a_batch, BK, BM);
     CUtensorMap map_b = p.b_mn ? make_map_bf16(g.b, g.n, g.k, g.batch, ldb, g.b_batch, 64, BK)
-                               : make_map_bf16(g.b, g.k, g.n, g.batch, ldb, g.b_batch, BK, p.bn);
+                               : make_map_bf16(g.b, g.k, g.n, g.batch, ldb, g.b_batch, BK, bn_local);
     const int element = p.out_fp32 ? 4 : 2;
     CUtensorMap map_c = make_map(g.c, element, g.n, g.m, g.batch, g.ldc, g.c_batch, 128 / element, 32);
-    CUtensorMap map_c2 = g.c2 ? make_map(g.c2, element, g.n, g.m, g.batch, g.ldc, g.c_batch, 128 / element, 32) : map_c;
-    CUtensorMap map_r = g.r ? make_map(g.r, element, g.n, g.m, g.batch, g.ldr, g.r_batch, 128 / element, 32) : map_c;
     long long work = tiles * p.splits;
-    int grid = int(work < sms ? work : sms);
+    const int slots = sms / unit;
+    int grid = int(work < slots ? work : slots) * unit;
     auto launch = [&](auto kernel) {
         // The opt-in shared-memory size is an attribute of each instantiation on each device.
         static std::mutex guard;
@@ -605,22 +694,36 @@ void launch_gemm_tc(const GemmArgs &g, int sms, StepCounters *counters, cudaStre
                 mask |= 1ull << (device & 63);
             }
         }
-        kernel<<<grid, Threads, shared, s>>>(map_a, map_b, map_c, map_c2, map_r, p);
+        cudaLaunchConfig_t config{};
+        config.gridDim = dim3(grid), config.blockDim = dim3(Threads);
+        config.dynamicSmemBytes = shared, config.stream = s;
+        cudaLaunchAttribute cluster{};
+        cluster.id = cudaLaunchAttributeClusterDimension;
+        cluster.val.clusterDim.x = unit, cluster.val.clusterDim.y = 1, cluster.val.clusterDim.z = 1;
+        config.attrs = &cluster, config.numAttrs = 1;
+        CHECK_CUDA(cudaLaunchKernelEx(&config, kernel, map_a, map_b, map_c, map_c, map_c, p));
     };
-    if (p.out_fp32) {
-        if (g.epilogue == Epilogue::Axpby)
-            launch(gemm_tc_kernel<int(Epilogue::Axpby), true>);
-        else
-            launch(gemm_tc_kernel<int(Epilogue::Store), true>);
-    } else {
-        switch (g.epilogue) {
-        case Epilogue::Store: launch(gemm_tc_kernel<int(Epilogue::Store), false>); break;
-        case Epilogue::Residual: launch(gemm_tc_kernel<int(Epilogue::Residual), false>); break;
-        case Epilogue::GeluDual: launch(gemm_tc_kernel<int(Epilogue::GeluDual), false>); break;
-        case Epilogue::GeluGrad: launch(gemm_tc_kernel<int(Epilogue::GeluGrad), false>); break;
-        case Epilogue::Axpby: launch(gemm_tc_kernel<int(Epilogue::Axpby), false>); break;
+    auto launch_kind = [&](auto pair_tag) {
+        constexpr bool P = decltype(pair_tag)::value;
+        if (p.out_fp32) {
+            if (g.epilogue == Epilogue::Axpby)
+                launch(gemm_tc_kernel<int(Epilogue::Axpby), true, P>);
+            else
+                launch(gemm_tc_kernel<int(Epilogue::Store), true, P>);
+        } else {
+            switch (g.epilogue) {
+            case Epilogue::Store: launch(gemm_tc_kernel<int(Epilogue::Store), false, P>); break;
+            case Epilogue::Residual: launch(gemm_tc_kernel<int(Epilogue::Residual), false, P>); break;
+            case Epilogue::GeluDual: launch(gemm_tc_kernel<int(Epilogue::GeluDual), false, P>); break;
+            case Epilogue::GeluGrad: launch(gemm_tc_kernel<int(Epilogue::GeluGrad), false, P>); break;
+            case Epilogue::Axpby: launch(gemm_tc_kernel<int(Epilogue::Axpby), false, P>); break;
+            }
         }
-    }
+    };
+    if (pair)
+        launch_kind(std::true_type{});
+    else
+        launch_kind(std::false_type{});
     CHECK_CUDA(cudaGetLastError());
 }
 
@@ -662,7 +765,7 @@ void launch_weight_gradient_static(const void *dy, const void *x, float *dw, int
     CHECK_CUDA(cudaGetDevice(&device));
     if (device < 0 || device >= 64)
         throw std::runtime_error("weight gradient: device index out of range");
-    auto kernel = gemm_tc_kernel<int(Epilogue::Store), true>;
+    auto kernel = gemm_tc_kernel<int(Epilogue::Store), true, false>;
     if (!static_scratch_address[device]) { // set-up, once per device, with that device current
         void *address = nullptr;
         CHECK_CUDA(cudaGetSymbolAddress(&address, static_scratch));

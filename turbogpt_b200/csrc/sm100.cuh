@@ -248,6 +248,61 @@ __device__ __forceinline__ void tcgen05_mma_bf16_ts(uint32_t d_tmem, uint32_t a_
                  : "memory");
 }
 
+// ---- CTA pairs (cluster of two CTAs driving one M = 256 MMA, cta_group::2) ----
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// Address of the same shared-memory location in CTA `rank` of the cluster (shared::cluster window).
+__device__ __forceinline__ uint32_t cluster_address(uint32_t local_address, uint32_t rank) {
+    uint32_t a;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(a) : "r"(local_address), "r"(rank));
+    return a;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Arrive on an mbarrier of another CTA of the cluster.
+__device__ __forceinline__ void mbarrier_arrive_cluster(uint32_t cluster_bar) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
+}
+// Tile load into this CTA's shared memory whose completion is counted on an mbarrier that may live
+// in the pair's other CTA (`cluster_bar` is a shared::cluster address).
+__device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const CUtensorMap *map, int x, int y, int z,
+                                                 uint32_t cluster_bar) {
+    asm volatile("cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes "
+                 "[%0], [%1, {%3, %4, %5}], [%2];" ::"r"(dst),
+                 "l"(reinterpret_cast<uint64_t>(map)), "r"(cluster_bar), "r"(x), "r"(y), "r"(z)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t result_slot, uint32_t columns) { // one warp in each CTA
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(result_slot),
+                 "r"(columns)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t address, uint32_t columns) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(address), "r"(columns) : "memory");
+}
+// Issued by the pair's leader: D (128 rows in each CTA's tensor memory) (+)= A (128 rows from each
+// CTA's shared memory) * B (N/2 columns from each CTA's shared memory).
+__device__ __forceinline__ void tcgen05_mma_bf16_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                                      uint32_t instruction, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+                 "l"(a_desc), "l"(b_desc), "r"(instruction), "r"(accumulate)
+                 : "memory");
+}
+// Arrives on one mbarrier (a shared::cluster address, in either CTA) when the pair's MMAs issued so
+// far have completed.
+__device__ __forceinline__ void tcgen05_commit_pair(uint32_t cluster_bar) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_bar)
+                 : "memory");
+}
+
 // ---- descriptors ----
 // Shared-memory matrix descriptor for 128-byte-swizzled BF16 tiles (version 1 = Blackwell).
 //   K-major  (rows of 64 K-elements = 128 B, 8-row atoms of 1024 B): SBO = 1024 B between atoms.
