@@ -116,3 +116,32 @@ def test_training_loss_curve_follows_oracle():
         actual = engine.training_losses(steps).mean(1)
     np.testing.assert_allclose(actual, np.array(expected), rtol=.01)
     assert actual[-1] < actual[0]
+
+
+def test_muon_on_the_tensor_core_path():
+    """Muon (Nesterov momentum, BF16 Newton-Schulz) on hidden matrices large enough for the batched
+    tcgen05 GEMMs, AdamW on the rest, against the CPU oracle: the configuration of the larger
+    BASELINE run (Muon on 2-D weights, AdamW on embeddings and norms)."""
+    depth, width, heads, hidden = 2, 256, 4, 512
+    arch = Arch.gpt(depth, width, heads, hidden)
+    model = Model(arch, seed=3)
+    w = model.flat()
+    base = Config(depth=depth, context=64, batch=4, clip=1.0, ns_steps=5)
+    ex = ConfigEx.gpt(base, width, heads, hidden, hidden_optimizer=bridge.HIDDEN_MUON)
+    hyper = Hyper(clip=1.0)
+    rng = np.random.default_rng(192)
+    for flags in (0, bridge.FLAG_NO_TENSOR_CORES):
+        ex.flags = flags
+        opt = Optimizer(arch, hyper, w, hidden="muon")
+        with Native(ex) as engine:
+            engine.set_weights(w)
+            for _ in range(3):
+                grad = (rng.standard_normal(engine.count) * .01).astype(np.float32)
+                engine.optimizer_test(grad, 1)
+                opt.step(grad)
+            actual = engine.weights()
+        mask = np.concatenate([np.full(int(np.prod(s)), not (len(s) == 2 and n.split(".")[-1] not in ("embedding", "head")))
+                               for n, s in specification(arch)])
+        assert relative(actual[mask] - w[mask], opt.w[mask] - w[mask]) < 1e-4
+        np.testing.assert_allclose(actual[mask], opt.w[mask], atol=2e-6, rtol=2e-5)
+        assert relative(actual - w, opt.w - w) < .04  # verify.py:101's bound for the Muon part

@@ -6,9 +6,10 @@
 // keys with TMA (two stages); warp 1 issues tcgen05.mma: S = Q K^T into tensor memory, then
 // O_blk = P V with P read back from tensor memory as the A operand; warps 2-5 own one query
 // row per thread (the TMEM lane), so the online-softmax row maximum and sum are thread-local:
-// two passes over S in TMEM (max, then exp2 and BF16 packing), P written to TMEM, the running
-// output kept in registers and rescaled when the maximum moves.  Two CTAs share an SM (256 TMEM
-// columns and 80 KB of shared memory each), so one CTA's exponentials overlap the other's MMAs.
+// one pass over S (128 registers), exp2 and BF16 packing, P written to TMEM; the output accumulates
+// in tensor memory and is rescaled only when the row maximum has grown by more than 2^8.  Two CTAs
+// share an SM (256 TMEM columns and 83 KB of shared memory each), so one CTA's exponentials overlap
+// the other's MMAs.
 #include "device_utils.cuh"
 #include "sm100.cuh"
 
@@ -117,9 +118,9 @@ flash_forward_kernel(const __grid_constant__ CUtensorMap map_qkv, ForwardParams 
                 tcgen05_fence_after();
                 const uint32_t v_tile = smem_kv + (j & 1) * 2 * TileBytes + TileBytes;
 #pragma unroll
-                for (int ks = 0; ks < BlockN / 16; ++ks) // O_blk = P V_j: eight 16-key steps
+                for (int ks = 0; ks < BlockN / 16; ++ks) // O += P V_j: eight 16-key steps
                     tcgen05_mma_bf16_ts(tmem_o, tmem_p + ks * 8, smem_descriptor(v_tile + ks * 2048, 8192, 1024),
-                                        idesc_o, ks > 0);
+                                        idesc_o, (j > 0 || ks > 0) ? 1u : 0u);
                 tcgen05_commit(o_full);
                 tcgen05_commit(kv_empty0 + 8 * (j & 1)); // K_j and V_j are no longer read
                 if (j + 1 < blocks) {
@@ -136,99 +137,112 @@ flash_forward_kernel(const __grid_constant__ CUtensorMap map_qkv, ForwardParams 
         const int row = quarter * 32 + lane;              // query row inside the tile = TMEM lane
         const int position = tile * BlockM + row;          // position inside the sequence
         const uint32_t lane_base = uint32_t(quarter * 32) << 16;
-        float o[HeadSize];
-#pragma unroll
-        for (int i = 0; i < HeadSize; ++i)
-            o[i] = 0.f;
-        float running_max = -CUDART_INF_F, running_sum = 0.f;
+        // The output accumulates in tensor memory across key blocks.  Probabilities are taken
+        // relative to a reference maximum that is only moved (and the output rescaled) when the true
+        // maximum has grown by more than 2^8: values stay inside BF16/FP32 range and the final
+        // division by the row sum, accumulated with the same reference, makes the result exact.
+        float reference_max = -CUDART_INF_F, running_sum = 0.f;
         bool ok = true;
         for (int j = 0; j < blocks; ++j) {
             ok = mbarrier_wait(s_full, j & 1, abort_flag, p.counters, 206);
             if (!ok)
                 break;
             tcgen05_fence_after();
-            const bool diagonal = j == tile;
-            // Pass 1: row maximum of the raw scores.
-            float block_max = -CUDART_INF_F;
-#pragma unroll
-            for (int c = 0; c < BlockN / 32; ++c) {
-                uint32_t r[32];
-                tmem_load_32x32_async(tmem_s + lane_base + c * 32, r);
-                tmem_wait_load(r);
+            uint32_t s0[32], s1[32], s2[32], s3[32];
+            tmem_load_32x32_async(tmem_s + lane_base, s0);
+            tmem_load_32x32_async(tmem_s + lane_base + 32, s1);
+            tmem_load_32x32_async(tmem_s + lane_base + 64, s2);
+            tmem_load_32x32_async(tmem_s + lane_base + 96, s3);
+            tmem_wait_load(s0);
+            tmem_wait_load(s1);
+            tmem_wait_load(s2);
+            tmem_wait_load(s3);
+            if (j == tile) { // diagonal block: keys after the query do not exist
 #pragma unroll
                 for (int i = 0; i < 32; ++i) {
-                    float s = __uint_as_float(r[i]);
-                    if (diagonal && c * 32 + i > row)
-                        s = -CUDART_INF_F;
-                    block_max = fmaxf(block_max, s);
+                    if (i > row) s0[i] = 0xff800000u;
+                    if (32 + i > row) s1[i] = 0xff800000u;
+                    if (64 + i > row) s2[i] = 0xff800000u;
+                    if (96 + i > row) s3[i] = 0xff800000u;
                 }
             }
-            const float new_max = fmaxf(running_max, block_max);
-            const float correction = fast_exp2((running_max - new_max) * p.scale_log2);
-            const float offset = new_max * p.scale_log2;
-            // The previous block's P V product: add it, then bring everything to the new maximum.
+            float block_max = -CUDART_INF_F;
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+                block_max = fmaxf(fmaxf(block_max, fmaxf(__uint_as_float(s0[i]), __uint_as_float(s1[i]))),
+                                  fmaxf(__uint_as_float(s2[i]), __uint_as_float(s3[i])));
+            // All earlier P V products must have completed before P is overwritten or O rescaled.
             if (j > 0) {
                 ok = mbarrier_wait(o_full, (j - 1) & 1, abort_flag, p.counters, 207);
                 if (!ok)
                     break;
                 tcgen05_fence_after();
-#pragma unroll
-                for (int c = 0; c < HeadSize / 32; ++c) {
-                    uint32_t r[32];
-                    tmem_load_32x32_async(tmem_o + lane_base + c * 32, r);
-                    tmem_wait_load(r);
+            }
+            const bool grow = (block_max - reference_max) * p.scale_log2 > 8.f; // also true for j == 0
+            if (__any_sync(0xffffffffu, grow) && j > 0) {
+                const float new_max = grow ? block_max : reference_max;
+                const float correction = fast_exp2((reference_max - new_max) * p.scale_log2);
+                running_sum *= correction;
+#pragma unroll 1
+                for (int half = 0; half < 2; ++half) { // 32 columns at a time keeps the register count down
+                    uint32_t a[32];
+                    tmem_load_32x32_async(tmem_o + lane_base + half * 32, a);
+                    tmem_wait_load(a);
 #pragma unroll
                     for (int i = 0; i < 32; ++i)
-                        o[c * 32 + i] = (o[c * 32 + i] + __uint_as_float(r[i])) * correction;
+                        a[i] = __float_as_uint(__uint_as_float(a[i]) * correction);
+                    tmem_store_32x32(tmem_o + lane_base + half * 32, a);
                 }
             }
-            // Pass 2: probabilities relative to the new maximum, packed to BF16 pairs in TMEM.
+            if (grow)
+                reference_max = block_max;
+            const float offset = reference_max * p.scale_log2;
             float block_sum = 0.f;
-#pragma unroll
-            for (int half = 0; half < 2; ++half) {
+            {
                 uint32_t packed[32];
 #pragma unroll
-                for (int c = 0; c < 2; ++c) {
-                    uint32_t r[32];
-                    tmem_load_32x32_async(tmem_s + lane_base + (half * 2 + c) * 32, r);
-                    tmem_wait_load(r);
-#pragma unroll
-                    for (int i = 0; i < 32; i += 2) {
-                        const int k = (half * 2 + c) * 32 + i;
-                        float p0 = fast_exp2(fmaf(__uint_as_float(r[i]), p.scale_log2, -offset));
-                        float p1 = fast_exp2(fmaf(__uint_as_float(r[i + 1]), p.scale_log2, -offset));
-                        if (diagonal) {
-                            p0 = k > row ? 0.f : p0;
-                            p1 = k + 1 > row ? 0.f : p1;
-                        }
-                        block_sum += p0 + p1;
-                        packed[c * 16 + i / 2] = pack_bf16(p0, p1);
-                    }
+                for (int i = 0; i < 32; i += 2) {
+                    float p0 = fast_exp2(fmaf(__uint_as_float(s0[i]), p.scale_log2, -offset));
+                    float p1 = fast_exp2(fmaf(__uint_as_float(s0[i + 1]), p.scale_log2, -offset));
+                    float p2 = fast_exp2(fmaf(__uint_as_float(s1[i]), p.scale_log2, -offset));
+                    float p3 = fast_exp2(fmaf(__uint_as_float(s1[i + 1]), p.scale_log2, -offset));
+                    block_sum += (p0 + p1) + (p2 + p3);
+                    packed[i / 2] = pack_bf16(p0, p1);
+                    packed[16 + i / 2] = pack_bf16(p2, p3);
                 }
-                tmem_store_32x32(tmem_p + lane_base + half * 32, packed);
+                tmem_store_32x32(tmem_p + lane_base, packed);
+            }
+            {
+                uint32_t packed[32];
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                    float p0 = fast_exp2(fmaf(__uint_as_float(s2[i]), p.scale_log2, -offset));
+                    float p1 = fast_exp2(fmaf(__uint_as_float(s2[i + 1]), p.scale_log2, -offset));
+                    float p2 = fast_exp2(fmaf(__uint_as_float(s3[i]), p.scale_log2, -offset));
+                    float p3 = fast_exp2(fmaf(__uint_as_float(s3[i + 1]), p.scale_log2, -offset));
+                    block_sum += (p0 + p1) + (p2 + p3);
+                    packed[i / 2] = pack_bf16(p0, p1);
+                    packed[16 + i / 2] = pack_bf16(p2, p3);
+                }
+                tmem_store_32x32(tmem_p + lane_base + 32, packed);
             }
             tmem_wait_store();
             tcgen05_fence_before();
             __syncwarp();
             if (lane == 0)
                 mbarrier_arrive(p_full);
-            running_sum = running_sum * correction + block_sum;
-            running_max = new_max;
+            running_sum += block_sum;
         }
         if (ok)
             ok = mbarrier_wait(o_full, (blocks - 1) & 1, abort_flag, p.counters, 208);
         if (ok) {
             tcgen05_fence_after();
             const float inverse = 1.f / running_sum;
-#pragma unroll
-            for (int c = 0; c < HeadSize / 32; ++c) {
-                uint32_t r[32];
-                tmem_load_32x32_async(tmem_o + lane_base + c * 32, r);
-                tmem_wait_load(r);
-#pragma unroll
-                for (int i = 0; i < 32; ++i)
-                    o[c * 32 + i] = (o[c * 32 + i] + __uint_as_float(r[i])) * inverse;
-            }
+            uint32_t a[32], c[32];
+            tmem_load_32x32_async(tmem_o + lane_base, a);
+            tmem_load_32x32_async(tmem_o + lane_base + 32, c);
+            tmem_wait_load(a);
+            tmem_wait_load(c);
             if (position < p.context) {
                 bf16 *out = p.out + (int64_t(row0) + position) * p.width + h * HeadSize;
 #pragma unroll
@@ -236,12 +250,12 @@ flash_forward_kernel(const __grid_constant__ CUtensorMap map_qkv, ForwardParams 
                     float v[8];
 #pragma unroll
                     for (int i = 0; i < 8; ++i)
-                        v[i] = o[g * 8 + i];
+                        v[i] = __uint_as_float(g < 4 ? a[g * 8 + i] : c[(g - 4) * 8 + i]) * inverse;
                     store8(out + g * 8, v);
                 }
                 // natural-log sum-exp of the scaled scores
                 p.lse[(int64_t(b) * p.heads + h) * p.context + position] =
-                    (running_max * p.scale_log2 + log2f(running_sum)) * 0.6931471805599453f;
+                    (reference_max * p.scale_log2 + log2f(running_sum)) * 0.6931471805599453f;
             }
         }
     }

@@ -91,8 +91,77 @@ __global__ void embedding_backward_kernel(const T *__restrict__ dhidden, const u
         }
     }
 }
+// Sliced variant for wide models: block (value, slice) sums the rows of its token slice whose byte
+// equals `value` (warp w scans the w-th eighth of the slice in order, lanes hold 8 columns per 256),
+// warps are added in order through shared memory, slices in order by the second kernel.
+template <class T>
+__global__ void __launch_bounds__(256) embedding_backward_slices_kernel(const T *__restrict__ dhidden,
+                                                                        const uint8_t *__restrict__ x,
+                                                                        float *__restrict__ partial, int tokens,
+                                                                        int width) {
+    extern __shared__ float sums[]; // [8 warps][width]
+    const int value = blockIdx.x, slice = blockIdx.y, lane = threadIdx.x % 32, warp = threadIdx.x / 32;
+    const int per_slice = (tokens + gridDim.y - 1) / gridDim.y;
+    const int per_warp = ((per_slice + 7) / 8 + 31) / 32 * 32;
+    const int begin = slice * per_slice + warp * per_warp;
+    const int end = min(min(begin + per_warp, (slice + 1) * per_slice), tokens);
+    float acc[4][8] = {};
+    for (int t0 = begin; t0 < end; t0 += 32) {
+        const int t = t0 + lane;
+        unsigned hits = __ballot_sync(0xffffffffu, t < end && x[t] == value);
+        while (hits) {
+            const int bit = __ffs(hits) - 1;
+            hits &= hits - 1;
+            const T *row = dhidden + int64_t(t0 + bit) * width;
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+                const int c = (v * 32 + lane) * 8;
+                if (c < width) {
+                    float r[8];
+                    load8(row + c, r);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j)
+                        acc[v][j] += r[j];
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int v = 0; v < 4; ++v) {
+        const int c = (v * 32 + lane) * 8;
+        if (c < width)
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                sums[warp * width + c + j] = acc[v][j];
+    }
+    __syncthreads();
+    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+        float total = 0;
+        for (int w = 0; w < 8; ++w)
+            total += sums[w * width + c];
+        partial[(int64_t(slice) * Vocabulary + value) * width + c] = total;
+    }
+}
+__global__ void embedding_backward_sum_kernel(const float *partial, float *grad, int width, int slices,
+                                              bool accumulate) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= Vocabulary * width)
+        return;
+    float total = accumulate ? grad[i] : 0.f;
+    for (int s = 0; s < slices; ++s)
+        total += partial[int64_t(s) * Vocabulary * width + i];
+    grad[i] = total;
+}
 void launch_embedding_backward(Dtype t, const void *dhidden, const uint8_t *x, float *grad, int tokens,
-                               int width, bool accumulate, cudaStream_t s) {
+                               int width, bool accumulate, float *scratch, cudaStream_t s) {
+    if (scratch && width <= 1024 && tokens >= 4096) {
+        DISPATCH(t, (embedding_backward_slices_kernel<T><<<dim3(Vocabulary, EmbeddingSlices), 256,
+                                                          8 * width * sizeof(float), s>>>(
+                        (const T *)dhidden, x, scratch, tokens, width)));
+        embedding_backward_sum_kernel<<<(Vocabulary * width + 255) / 256, 256, 0, s>>>(scratch, grad, width,
+                                                                                     EmbeddingSlices, accumulate);
+        return;
+    }
     int threads = width >= 256 ? 256 : (width + 31) / 32 * 32;
     DISPATCH(t, (embedding_backward_kernel<T><<<Vocabulary, threads, 0, s>>>((const T *)dhidden, x, grad, tokens,
                                                                            width, accumulate)));
@@ -190,16 +259,14 @@ template <int V> __device__ __forceinline__ void row_moments(int kind, const flo
             centred += (x[v][j] - mean) * (x[v][j] - mean);
     inv = rsqrtf(warp_sum(centred) / width + 1e-5f);
 }
-template <class T, int V> __global__ void __launch_bounds__(256) norm_rows_kernel(NormArgs a) {
+template <class T, int V> __global__ void __launch_bounds__(256, 4) norm_rows_kernel(NormArgs a) {
+    __shared__ __align__(16) float sw[V * 256], sb[V * 256]; // FP32 scale and bias, shared by the block's rows
     const int lane = threadIdx.x % 32, warps = blockDim.x / 32;
-    float w[V][8], b[V][8];
-#pragma unroll
-    for (int v = 0; v < V; ++v) {
-        const int c = (v * 32 + lane) * 8;
-        load_scale8(a.scale_high, a.scale_low, c, w[v]);
-        if (a.kind == TG_NORM_LAYER)
-            load_scale8(a.bias_high, a.bias_low, c, b[v]);
+    for (int c = threadIdx.x; c < V * 256; c += blockDim.x) {
+        sw[c] = join_weight(a.scale_high[c], a.scale_low[c]);
+        sb[c] = a.kind == TG_NORM_LAYER ? join_weight(a.bias_high[c], a.bias_low[c]) : 0.f;
     }
+    __syncthreads();
     for (int row = blockIdx.x * warps + threadIdx.x / 32; row < a.rows; row += gridDim.x * warps) {
         const T *x = (const T *)a.x + int64_t(row) * a.width;
         T *y = (T *)a.y + int64_t(row) * a.width;
@@ -211,16 +278,18 @@ template <class T, int V> __global__ void __launch_bounds__(256) norm_rows_kerne
         row_moments<V>(a.kind, v, a.width, mean, inv);
 #pragma unroll
         for (int k = 0; k < V; ++k) {
-            float out[8];
+            float out[8], w[8], b[8];
+            load8(sw + (k * 32 + lane) * 8, w);
+            load8(sb + (k * 32 + lane) * 8, b);
 #pragma unroll
             for (int j = 0; j < 8; ++j)
-                out[j] = a.kind == TG_NORM_RMS ? v[k][j] * inv * w[k][j] : (v[k][j] - mean) * inv * w[k][j] + b[k][j];
+                out[j] = a.kind == TG_NORM_RMS ? v[k][j] * inv * w[j] : (v[k][j] - mean) * inv * w[j] + b[j];
             store8(y + (k * 32 + lane) * 8, out);
         }
     }
 }
 template <class T> static void launch_norm_rows(const NormArgs &a, cudaStream_t s) {
-    const int blocks = blocks_for(a.rows, 8, 148 * 8);
+    const int blocks = blocks_for(a.rows, 8, 148 * 4);
     switch (a.width / 256) {
     case 1: norm_rows_kernel<T, 1><<<blocks, 256, 0, s>>>(a); break;
     case 2: norm_rows_kernel<T, 2><<<blocks, 256, 0, s>>>(a); break;
@@ -320,16 +389,17 @@ __global__ void __launch_bounds__(256) norm_backward_reduce_kernel(const float *
 // scale/bias gradient sums of its own columns over all rows of its warp, warps are summed in
 // order through shared memory, blocks in order by the reduce kernel: deterministic.
 template <class T, int V> __global__ void __launch_bounds__(256, 2) norm_backward_rows_kernel(NormBackwardArgs a) {
-    extern __shared__ float sums[]; // [warps][2][width]
+    extern __shared__ float sums[]; // [warps][2][width]; first `width` floats hold the scale during the row loop
     const int lane = threadIdx.x % 32, warp = threadIdx.x / 32, warps = blockDim.x / 32;
-    float w[V][8], dw[V][8], db[V][8];
+    float dw[V][8], db[V][8];
+    for (int c = threadIdx.x; c < V * 256; c += blockDim.x)
+        sums[c] = join_weight(a.scale_high[c], a.scale_low[c]);
+    __syncthreads();
 #pragma unroll
-    for (int v = 0; v < V; ++v) {
-        load_scale8(a.scale_high, a.scale_low, (v * 32 + lane) * 8, w[v]);
+    for (int v = 0; v < V; ++v)
 #pragma unroll
         for (int j = 0; j < 8; ++j)
             dw[v][j] = db[v][j] = 0.f;
-    }
     for (int row = blockIdx.x * warps + warp; row < a.rows; row += gridDim.x * warps) {
         const int64_t offset = int64_t(row) * a.width;
         float x[V][8], g[V][8];
@@ -342,16 +412,20 @@ template <class T, int V> __global__ void __launch_bounds__(256, 2) norm_backwar
         row_moments<V>(a.kind, x, a.width, mean, inv);
         float sum_dz = 0, sum_dzz = 0;
 #pragma unroll
-        for (int v = 0; v < V; ++v)
+        for (int v = 0; v < V; ++v) {
+            float w[8];
+            load8(sums + (v * 32 + lane) * 8, w);
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
-                const float z = (x[v][j] - mean) * inv, dz = g[v][j] * w[v][j];
+                const float z = (x[v][j] - mean) * inv, dz = g[v][j] * w[j];
                 x[v][j] = z; // keep the normalised value
                 sum_dz += dz;
                 sum_dzz += dz * z;
                 dw[v][j] += g[v][j] * z;
                 db[v][j] += g[v][j];
+                g[v][j] = dz; // keep dy * scale
             }
+        }
         sum_dzz = warp_sum(sum_dzz) / a.width;
         sum_dz = a.kind == TG_NORM_LAYER ? warp_sum(sum_dz) / a.width : 0.f;
 #pragma unroll
@@ -359,7 +433,7 @@ template <class T, int V> __global__ void __launch_bounds__(256, 2) norm_backwar
             float out[8];
 #pragma unroll
             for (int j = 0; j < 8; ++j)
-                out[j] = (g[v][j] * w[v][j] - sum_dz - x[v][j] * sum_dzz) * inv;
+                out[j] = (g[v][j] - sum_dz - x[v][j] * sum_dzz) * inv;
             if (a.residual_in) {
                 float r[8];
                 load8((const T *)a.residual_in + offset + (v * 32 + lane) * 8, r);
@@ -370,6 +444,7 @@ template <class T, int V> __global__ void __launch_bounds__(256, 2) norm_backwar
             store8((T *)a.dx + offset + (v * 32 + lane) * 8, out);
         }
     }
+    __syncthreads(); // every warp is done reading the scale
 #pragma unroll
     for (int v = 0; v < V; ++v)
 #pragma unroll

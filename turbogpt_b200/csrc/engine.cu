@@ -149,6 +149,8 @@ void Engine::initialize() {
     allocate(attention_scratch, M * c.heads, false);
     norm_blocks = norm_backward_blocks(tokens, sms);
     allocate(norm_partial, size_t(norm_blocks) * 2 * W, false);
+    if (W <= 1024 && tokens >= 4096)
+        allocate(embedding_partial, size_t(EmbeddingSlices) * Vocabulary * W, false);
     sumsq_blocks = sms * 2;
     allocate(sumsq_partial, sumsq_blocks);
 
@@ -504,7 +506,8 @@ void Engine::backward() {
         exchange_bucket(p.attention_norm, layer_end, l);
     }
     run(FEmbeddingBackward, [&] {
-        launch_embedding_backward(act, dh, x, gradient + layout.embedding, M, W, c.tied != 0, stream);
+        launch_embedding_backward(act, dh, x, gradient + layout.embedding, M, W, c.tied != 0, embedding_partial,
+                                  stream);
     });
     exchange_bucket(layout.embedding, layout.embedding + int64_t(Vocabulary) * W, depth + 1);
     finish_exchange();

@@ -63,7 +63,7 @@ struct Engine {
          *dqkv = nullptr;
     float *attention_scratch = nullptr; // dt (arg-max) or delta (softmax)
     float *token_losses = nullptr, *loss_history = nullptr, *norm_partial = nullptr, *sumsq_partial = nullptr,
-          *logits_fp32 = nullptr, *mean_loss = nullptr;
+          *logits_fp32 = nullptr, *mean_loss = nullptr, *embedding_partial = nullptr;
     int norm_blocks = 0, sumsq_blocks = 0;
     StepCounters *counters = nullptr;
     TgStepRates *schedule = nullptr;

@@ -31,8 +31,10 @@ void launch_embedding(Dtype t, const void *table, const uint8_t *x, void *hidden
                       cudaStream_t s);
 // grad[x[t]*width + c] += dhidden[t, c] in FP32 (reference cuda/model.cuh:96-97), deterministic:
 // one CTA per byte value scans the tokens in order.
+// `scratch`: EmbeddingSlices x 256 x width floats (nullptr: single-pass kernel for small shapes).
+constexpr int EmbeddingSlices = 8;
 void launch_embedding_backward(Dtype t, const void *dhidden, const uint8_t *x, float *grad, int tokens,
-                               int width, bool accumulate, cudaStream_t s);
+                               int width, bool accumulate, float *scratch, cudaStream_t s);
 
 // ---- norms (reference cuda/ops.cuh:56-80) ----
 struct NormArgs {
