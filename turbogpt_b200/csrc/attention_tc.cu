@@ -279,7 +279,8 @@ flash_forward_kernel(const __grid_constant__ CUtensorMap map_qkv, ForwardParams 
 //                  A operands in tensor memory for dV += P^T dO and dK += dS^T Q.
 // Both keep 256 TMEM columns and under 100 KB of shared memory, so two CTAs share an SM.
 // ------------------------------------------------------------------------------------------
-constexpr int BackwardThreads = 192, BackwardTmemColumns = 256, HalfTileBytes = 64 * HeadSize * 2; // 8 KB
+constexpr int BackwardThreads = 320, BackwardTmemColumns = 256, // warp 0 TMA, warp 1 MMA, 8 compute warps
+               HalfTileBytes = 64 * HeadSize * 2; // 8 KB
 constexpr int DqShared = 2 * TileBytes + 4 * HalfTileBytes + 1024 + 256;      // Q, dO + 2 x (K, V) blocks
 constexpr int DkvShared = 2 * TileBytes + 4 * HalfTileBytes + 1024 + 1024 + 256; // K, V + 2 x (Q, dO) + statistics
 
@@ -324,7 +325,7 @@ flash_dq_kernel(const __grid_constant__ CUtensorMap map_qkv128, const __grid_con
             mbarrier_init(kv_empty0 + 8 * s, 1);
         }
         mbarrier_init(s_full, 1);
-        mbarrier_init(ds_full, 4);
+        mbarrier_init(ds_full, 8);
         mbarrier_init(dq_done, 1);
         *abort_flag = 0;
         fence_barrier_init();
@@ -379,8 +380,9 @@ flash_dq_kernel(const __grid_constant__ CUtensorMap map_qkv128, const __grid_con
                     break;
                 tcgen05_fence_after();
 #pragma unroll
-                for (int ks = 0; ks < 64 / 16; ++ks) // dQ += dS K_j: four 16-key steps
-                    tcgen05_mma_bf16_ts(tmem_dq, tmem_s + ks * 8, smem_descriptor(k_tile + ks * 2048, 8192, 1024),
+                for (int ks = 0; ks < 64 / 16; ++ks) // dQ += dS K_j: four 16-key steps (dS: columns 0-15 and 32-47)
+                    tcgen05_mma_bf16_ts(tmem_dq, tmem_s + (ks / 2) * 32 + (ks % 2) * 8,
+                                        smem_descriptor(k_tile + ks * 2048, 8192, 1024),
                                         idesc_dq, (j > 0 || ks > 0) ? 1u : 0u);
                 tcgen05_commit(kv_empty0 + 8 * (j & 1));
             }
@@ -388,9 +390,11 @@ flash_dq_kernel(const __grid_constant__ CUtensorMap map_qkv128, const __grid_con
                 tcgen05_commit(dq_done);
         }
     } else {
-        const int quarter = warp % 4;
+        // Two warps share each 32-lane quarter: warp `half` takes score columns half*32 .. half*32+31
+        // and leaves its 16 packed dS columns at the start of its own column range.
+        const int quarter = warp % 4, half = (warp - 2) / 4;
         const int row = quarter * 32 + lane, position = tile * BlockM + row;
-        const uint32_t lane_base = uint32_t(quarter * 32) << 16;
+        const uint32_t lane_base = (uint32_t(quarter * 32) << 16) + half * 32;
         const bool valid = position < p.context;
         const int64_t stat = (int64_t(b) * p.heads + h) * p.context + position;
         const float lse2 = valid ? p.lse[stat] * 1.4426950408889634f : 0.f;
@@ -401,29 +405,25 @@ flash_dq_kernel(const __grid_constant__ CUtensorMap map_qkv128, const __grid_con
             if (!ok)
                 break;
             tcgen05_fence_after();
-            uint32_t s0[32], s1[32], d0[32], d1[32], packed[32];
-            load_columns_64(tmem_s + lane_base, s0, s1);
-            load_columns_64(tmem_dp + lane_base, d0, d1);
-            tmem_wait_load(s0);
-            tmem_wait_load(s1);
-            tmem_wait_load(d0);
-            tmem_wait_load(d1);
-            const bool masked_block = (j + 1) * 64 > position; // some keys of this block lie after the query
+            uint32_t sc[32], dp[32], packed[16];
+            tmem_load_32x32_async(tmem_s + lane_base, sc);
+            tmem_load_32x32_async(tmem_dp + lane_base, dp);
+            tmem_wait_load(sc);
+            tmem_wait_load(dp);
+            const int key0 = j * 64 + half * 32;
+            const bool masked_block = key0 + 32 > position; // some keys of this range lie after the query
 #pragma unroll
             for (int i = 0; i < 32; i += 2) {
-                float v[4];
+                float v[2];
 #pragma unroll
-                for (int u = 0; u < 4; ++u) {
-                    const uint32_t sr = u < 2 ? s0[i + u] : s1[i + u - 2], dr = u < 2 ? d0[i + u] : d1[i + u - 2];
-                    const int key = j * 64 + (u < 2 ? i + u : 32 + i + u - 2);
-                    float prob = fast_exp2(fmaf(__uint_as_float(sr), p.scale_log2, -lse2));
-                    float ds = prob * (__uint_as_float(dr) - delta) * p.scale;
-                    v[u] = (masked_block && key > position) || !valid ? 0.f : ds;
+                for (int u = 0; u < 2; ++u) {
+                    float prob = fast_exp2(fmaf(__uint_as_float(sc[i + u]), p.scale_log2, -lse2));
+                    float ds = prob * (__uint_as_float(dp[i + u]) - delta) * p.scale;
+                    v[u] = (masked_block && key0 + i + u > position) || !valid ? 0.f : ds;
                 }
                 packed[i / 2] = pack_bf16(v[0], v[1]);
-                packed[16 + i / 2] = pack_bf16(v[2], v[3]);
             }
-            tmem_store_32x32(tmem_s + lane_base, packed);
+            tmem_store_32x16(tmem_s + lane_base, packed);
             tmem_wait_store();
             tcgen05_fence_before();
             __syncwarp();
@@ -434,18 +434,17 @@ flash_dq_kernel(const __grid_constant__ CUtensorMap map_qkv128, const __grid_con
             ok = mbarrier_wait(dq_done, 0, abort_flag, p.counters, 306);
         if (ok) {
             tcgen05_fence_after();
-            uint32_t a[32], c[32];
-            load_columns_64(tmem_dq + lane_base, a, c);
+            uint32_t a[32];
+            tmem_load_32x32_async(tmem_dq + lane_base, a);
             tmem_wait_load(a);
-            tmem_wait_load(c);
             if (valid) {
-                bf16 *out = p.dqkv + (int64_t(row0) + position) * 3 * p.width + h * HeadSize;
+                bf16 *out = p.dqkv + (int64_t(row0) + position) * 3 * p.width + h * HeadSize + half * 32;
 #pragma unroll
-                for (int g = 0; g < 8; ++g) {
+                for (int g = 0; g < 4; ++g) {
                     float v[8];
 #pragma unroll
                     for (int i = 0; i < 8; ++i)
-                        v[i] = __uint_as_float(g < 4 ? a[g * 8 + i] : c[(g - 4) * 8 + i]);
+                        v[i] = __uint_as_float(a[g * 8 + i]);
                     store8(out + g * 8, v);
                 }
             }
@@ -489,7 +488,7 @@ flash_dkv_kernel(const __grid_constant__ CUtensorMap map_qkv128, const __grid_co
             mbarrier_init(qdo_empty0 + 8 * s, 1);
         }
         mbarrier_init(s_full, 1);
-        mbarrier_init(pd_full, 4);
+        mbarrier_init(pd_full, 8);
         mbarrier_init(acc_done, 1);
         *abort_flag = 0;
         fence_barrier_init();
@@ -546,11 +545,13 @@ flash_dkv_kernel(const __grid_constant__ CUtensorMap map_qkv128, const __grid_co
                 tcgen05_fence_after();
 #pragma unroll
                 for (int ks = 0; ks < 64 / 16; ++ks) // dV += P^T dO_i
-                    tcgen05_mma_bf16_ts(tmem_dv, tmem_s + ks * 8, smem_descriptor(do_tile + ks * 2048, 8192, 1024),
+                    tcgen05_mma_bf16_ts(tmem_dv, tmem_s + (ks / 2) * 32 + (ks % 2) * 8,
+                                        smem_descriptor(do_tile + ks * 2048, 8192, 1024),
                                         idesc_acc, (i > 0 || ks > 0) ? 1u : 0u);
 #pragma unroll
                 for (int ks = 0; ks < 64 / 16; ++ks) // dK += dS^T Q_i
-                    tcgen05_mma_bf16_ts(tmem_dk, tmem_dp + ks * 8, smem_descriptor(q_tile + ks * 2048, 8192, 1024),
+                    tcgen05_mma_bf16_ts(tmem_dk, tmem_dp + (ks / 2) * 32 + (ks % 2) * 8,
+                                        smem_descriptor(q_tile + ks * 2048, 8192, 1024),
                                         idesc_acc, (i > 0 || ks > 0) ? 1u : 0u);
                 tcgen05_commit(qdo_empty0 + 8 * (i & 1));
             }
@@ -558,28 +559,30 @@ flash_dkv_kernel(const __grid_constant__ CUtensorMap map_qkv128, const __grid_co
                 tcgen05_commit(acc_done);
         }
     } else {
-        const int quarter = warp % 4;
+        // Two warps share each 32-lane quarter and take 32 of the 64 query columns each; their packed
+        // P^T / dS^T columns sit at the start of their own column range (0-15 and 32-47).
+        const int quarter = warp % 4, half = (warp - 2) / 4;
         const int row = quarter * 32 + lane, key = tile * BlockN + row; // key position inside the sequence
-        const uint32_t lane_base = uint32_t(quarter * 32) << 16;
-        const int t128 = threadIdx.x - 64; // 0..127 among the compute threads
+        const uint32_t lane_base = (uint32_t(quarter * 32) << 16) + half * 32;
+        const int t256 = threadIdx.x - 64; // 0..255 among the compute threads
         const float *lse = p.lse + (int64_t(b) * p.heads + h) * p.context;
         const float *delta = p.delta + (int64_t(b) * p.heads + h) * p.context;
         bool ok = true;
         for (int i = 0; i < blocks; ++i) {
             const int q0 = (first_block + i) * 64;
             float *stats = statistics + (i & 1) * 128;
-            { // one statistic per thread: lse (scaled to base 2) for 64 queries, then delta
-                const int q = q0 + (t128 & 63);
+            if (t256 < 128) { // one statistic per thread: lse (scaled to base 2) for 64 queries, then delta
+                const int q = q0 + (t256 & 63);
                 float value = 0.f;
                 if (q < p.context)
-                    value = t128 < 64 ? lse[q] * 1.4426950408889634f : delta[q];
-                stats[t128] = value;
+                    value = t256 < 64 ? lse[q] * 1.4426950408889634f : delta[q];
+                stats[t256] = value;
             }
-            asm volatile("bar.sync 1, 128;" ::: "memory");
+            asm volatile("bar.sync 1, 256;" ::: "memory");
             bool ready = mbarrier_wait(s_full, i & 1, abort_flag, p.counters, 315);
-            // all four warps meet at the named barrier above every iteration: leave together
+            // all eight warps meet at the named barrier above every iteration: leave together
             uint32_t all_ready;
-            asm volatile("{\n\t.reg .pred a, c;\n\tsetp.ne.u32 a, %1, 0;\n\tbar.red.and.pred c, 2, 128, a;\n\t"
+            asm volatile("{\n\t.reg .pred a, c;\n\tsetp.ne.u32 a, %1, 0;\n\tbar.red.and.pred c, 2, 256, a;\n\t"
                          "selp.u32 %0, 1, 0, c;\n\t}"
                          : "=r"(all_ready)
                          : "r"(uint32_t(ready))
@@ -588,34 +591,30 @@ flash_dkv_kernel(const __grid_constant__ CUtensorMap map_qkv128, const __grid_co
             if (!ok)
                 break;
             tcgen05_fence_after();
-            uint32_t s0[32], s1[32], d0[32], d1[32], pp[32], pd[32];
-            load_columns_64(tmem_s + lane_base, s0, s1);
-            load_columns_64(tmem_dp + lane_base, d0, d1);
-            tmem_wait_load(s0);
-            tmem_wait_load(s1);
-            tmem_wait_load(d0);
-            tmem_wait_load(d1);
-            const bool edge = q0 < key + 1 || q0 + 64 > p.context; // causal diagonal or ragged end
+            uint32_t sc[32], dp[32], pp[16], pd[16];
+            tmem_load_32x32_async(tmem_s + lane_base, sc);
+            tmem_load_32x32_async(tmem_dp + lane_base, dp);
+            tmem_wait_load(sc);
+            tmem_wait_load(dp);
+            const int qa = q0 + half * 32; // first query of this warp's columns
+            const bool edge = qa < key + 1 || qa + 32 > p.context; // causal diagonal or ragged end
 #pragma unroll
             for (int c = 0; c < 32; c += 2) {
-                float pv[4], dv[4];
+                float pv[2], dv[2];
 #pragma unroll
-                for (int u = 0; u < 4; ++u) {
-                    const int col = u < 2 ? c + u : 32 + c + u - 2;
-                    const uint32_t sr = u < 2 ? s0[c + u] : s1[c + u - 2], dr = u < 2 ? d0[c + u] : d1[c + u - 2];
-                    float prob = fast_exp2(fmaf(__uint_as_float(sr), p.scale_log2, -stats[col]));
+                for (int u = 0; u < 2; ++u) {
+                    const int col = half * 32 + c + u;
+                    float prob = fast_exp2(fmaf(__uint_as_float(sc[c + u]), p.scale_log2, -stats[col]));
                     if (edge && (q0 + col < key || q0 + col >= p.context))
                         prob = 0.f;
                     pv[u] = prob;
-                    dv[u] = prob * (__uint_as_float(dr) - stats[64 + col]) * p.scale;
+                    dv[u] = prob * (__uint_as_float(dp[c + u]) - stats[64 + col]) * p.scale;
                 }
                 pp[c / 2] = pack_bf16(pv[0], pv[1]);
-                pp[16 + c / 2] = pack_bf16(pv[2], pv[3]);
                 pd[c / 2] = pack_bf16(dv[0], dv[1]);
-                pd[16 + c / 2] = pack_bf16(dv[2], dv[3]);
             }
-            tmem_store_32x32(tmem_s + lane_base, pp);
-            tmem_store_32x32(tmem_dp + lane_base, pd);
+            tmem_store_32x16(tmem_s + lane_base, pp);
+            tmem_store_32x16(tmem_dp + lane_base, pd);
             tmem_wait_store();
             tcgen05_fence_before();
             __syncwarp();
@@ -628,18 +627,18 @@ flash_dkv_kernel(const __grid_constant__ CUtensorMap map_qkv128, const __grid_co
             tcgen05_fence_after();
 #pragma unroll
             for (int which = 0; which < 2; ++which) { // dK then dV
-                uint32_t a[32], c[32];
-                load_columns_64((which == 0 ? tmem_dk : tmem_dv) + lane_base, a, c);
+                uint32_t a[32];
+                tmem_load_32x32_async((which == 0 ? tmem_dk : tmem_dv) + lane_base, a);
                 tmem_wait_load(a);
-                tmem_wait_load(c);
                 if (key < p.context) {
-                    bf16 *out = p.dqkv + (int64_t(row0) + key) * 3 * p.width + (which + 1) * p.width + h * HeadSize;
+                    bf16 *out = p.dqkv + (int64_t(row0) + key) * 3 * p.width + (which + 1) * p.width + h * HeadSize +
+                                half * 32;
 #pragma unroll
-                    for (int g = 0; g < 8; ++g) {
+                    for (int g = 0; g < 4; ++g) {
                         float v[8];
 #pragma unroll
                         for (int e = 0; e < 8; ++e)
-                            v[e] = __uint_as_float(g < 4 ? a[g * 8 + e] : c[(g - 4) * 8 + e]);
+                            v[e] = __uint_as_float(a[g * 8 + e]);
                         store8(out + g * 8, v);
                     }
                 }

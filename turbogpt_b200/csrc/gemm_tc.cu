@@ -56,19 +56,21 @@ struct TcParams {
     StepCounters *counters;
 };
 
-// erf by Abramowitz & Stegun 7.1.26 (|error| < 1.5e-7); the same exponential serves the
-// Gaussian term of the derivative.  z = x / sqrt(2).
+// Phi(x) = 0.5 (1 + erf(x / sqrt 2)) by Abramowitz & Stegun 7.1.26 (|error| < 3e-7) with every
+// constant folded: t = 1 / (1 + p |x| / sqrt 2), e = 2^(-x^2 log2(e) / 2), tail = 0.5 erfc = poly(t) t e.
+// Two SFU operations (rcp, ex2) and nine FMA-pipe operations; the exponential also gives the
+// Gaussian density of the derivative.
 __device__ __forceinline__ void gelu_terms(float x, float &cdf, float &density) {
-    const float z = fabsf(x) * 0.7071067811865475f;
-    const float t = __fdividef(1.f, fmaf(0.3275911f, z, 1.f));
-    const float e = __expf(-z * z);
-    float poly = fmaf(t, 1.061405429f, -1.453152027f);
-    poly = fmaf(t, poly, 1.421413741f);
-    poly = fmaf(t, poly, -0.284496736f);
-    poly = fmaf(t, poly, 0.254829592f);
-    const float tail = 0.5f * poly * t * e;       // 0.5 * erfc(|z|)
-    cdf = x >= 0.f ? 1.f - tail : tail;           // 0.5 * (1 + erf(z))
-    density = 0.3989422804014327f * e;            // exp(-x^2/2) / sqrt(2 pi)
+    float t, e;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(t) : "f"(fmaf(0.23164189f, fabsf(x), 1.f)));
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(-0.72134752f * x * x));
+    float poly = fmaf(t, 0.5307027145f, -0.7265760135f);
+    poly = fmaf(t, poly, 0.7107068705f);
+    poly = fmaf(t, poly, -0.142248368f);
+    poly = fmaf(t, poly, 0.127414796f);
+    const float tail = poly * t * e;
+    cdf = x >= 0.f ? 1.f - tail : tail;
+    density = 0.3989422804014327f * e; // exp(-x^2/2) / sqrt(2 pi)
 }
 __device__ __forceinline__ float fast_gelu(float x) {
     float cdf, density;
