@@ -86,7 +86,8 @@ enum { TG_HIDDEN_MUON = 0, TG_HIDDEN_ADAMW = 1 };
 enum { TG_PRECISION_BF16 = 0, TG_PRECISION_FP32 = 1 };
 enum { TG_FLAG_NO_TENSOR_CORES = 1, /* route every GEMM and attention through the plain CUDA-core kernels */
        TG_FLAG_PROFILE = 2,         /* time every kernel family with CUDA events (serialises nothing, disables graph replay) */
-       TG_FLAG_BF16_GRADIENT_EXCHANGE = 4 /* all-reduce gradients as BF16 instead of FP32 */ };
+       TG_FLAG_BF16_GRADIENT_EXCHANGE = 4, /* all-reduce gradients as BF16 instead of FP32 */
+       TG_FLAG_NO_GRAPH = 8         /* launch every kernel of tg_train directly instead of replaying a CUDA graph of the step */ };
 
 /* Replaces the compile-time "Width=16, heads=4" of config.h:4 and the hard-wired sizes of
  * model.h:20-34.  `base` keeps the reference's meaning.  struct_size must be

@@ -20,7 +20,7 @@ MLP_SWIGLU, MLP_GELU = 0, 1
 ROPE_NONE, ROPE_PARTIAL = 0, 1
 HIDDEN_MUON, HIDDEN_ADAMW = 0, 1
 PRECISION_BF16, PRECISION_FP32 = 0, 1
-FLAG_NO_TENSOR_CORES, FLAG_PROFILE, FLAG_BF16_GRADIENT_EXCHANGE = 1, 2, 4
+FLAG_NO_TENSOR_CORES, FLAG_PROFILE, FLAG_BF16_GRADIENT_EXCHANGE, FLAG_NO_GRAPH = 1, 2, 4, 8
 
 
 class Config(C.Structure):

@@ -207,6 +207,7 @@ void Engine::release() {
         cudaStreamSynchronize(exchange_stream);
     if (comm)
         Nccl::get().CommDestroy(comm);
+    drop_graph();
     for (auto &t : timed) {
         cudaEventDestroy(t.start);
         cudaEventDestroy(t.stop);
@@ -303,6 +304,7 @@ void Engine::get_weights(float *w) {
     CHECK_CUDA(cudaStreamSynchronize(stream));
 }
 void Engine::set_data(const uint8_t *bytes, int64_t size) {
+    drop_graph();
     set_device();
     if (size <= 8)
         throw std::runtime_error("Dataset needs at least 9 bytes");
@@ -316,6 +318,7 @@ void Engine::set_data(const uint8_t *bytes, int64_t size) {
     CHECK_CUDA(cudaStreamSynchronize(stream));
 }
 void Engine::set_onecycle(const TgOneCycle &s) {
+    drop_graph();
     set_device();
     if (schedule || step)
         throw std::runtime_error("Set OneCycle once, before training");
@@ -600,6 +603,13 @@ void Engine::one_step(RunMode mode) {
     optimize();
 }
 
+// The captured step holds raw pointers: it is dropped whenever one of them may change.
+void Engine::drop_graph() {
+    if (step_graph)
+        cudaGraphExecDestroy(step_graph);
+    step_graph = nullptr;
+}
+
 void Engine::train(int steps) {
     set_device();
     if (!data || steps < 1 || steps > MaxLaunchSteps)
@@ -610,8 +620,40 @@ void Engine::train(int steps) {
     if (schedule && step + uint64_t(steps) > uint64_t(schedule_steps))
         throw std::runtime_error("Training would exceed the OneCycle schedule");
     CHECK_CUDA(cudaMemsetAsync(&counters->iteration, 0, sizeof(int), stream));
-    for (int i = 0; i < steps; ++i)
-        one_step(RunMode::Train);
+    // A step reads everything that changes from device memory, so its kernel sequence is captured
+    // once (after one eager step has sized every workspace) and replayed as a CUDA graph.
+    const bool use_graph = !profile && !comm && !(config.flags & TG_FLAG_NO_GRAPH) && !getenv("TURBOGPT_NO_GRAPH");
+    for (int i = 0; i < steps; ++i) {
+        if (!use_graph || !graph_warm) {
+            one_step(RunMode::Train);
+            graph_warm = true;
+            continue;
+        }
+        if (step_graph && graph_generation != gemm_tc_workspace_generation())
+            drop_graph(); // the split-K workspace moved since the capture
+        if (!step_graph) {
+            graph_generation = gemm_tc_workspace_generation();
+            const int64_t before = launches;
+            cudaGraph_t graph = nullptr;
+            CHECK_CUDA(cudaStreamBeginCapture(stream, cudaStreamCaptureModeThreadLocal));
+            try {
+                one_step(RunMode::Train);
+            } catch (...) {
+                cudaStreamEndCapture(stream, &graph);
+                if (graph)
+                    cudaGraphDestroy(graph);
+                throw;
+            }
+            CHECK_CUDA(cudaStreamEndCapture(stream, &graph));
+            cudaError_t status = cudaGraphInstantiate(&step_graph, graph, 0);
+            cudaGraphDestroy(graph);
+            CHECK_CUDA(status);
+            graph_launches = launches - before;
+            launches = before;
+        }
+        CHECK_CUDA(cudaGraphLaunch(step_graph, stream));
+        launches += graph_launches;
+    }
     last_train_steps = steps;
     losses_reduced = false;
     step += steps;

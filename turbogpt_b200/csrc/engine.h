@@ -30,7 +30,7 @@ enum Family {
 extern const char *const family_names[FamilyCount];
 
 struct LayerActivations { // saved by forward for backward (reference cuda/types.cuh:40-44)
-    void *x, *normed1, *qkv, *attended, *middle, *normed2, *wide, *activated;
+    void *x, *normed1, *qkv, *attended, *middle, *normed2, *wide, *activated; // wide: gate|up, or gelu'(pre-activation)
     int *selected;
     float *gates, *derivatives, *lse;
 };
@@ -88,7 +88,11 @@ struct Engine {
     std::vector<cudaEvent_t> event_pool;
     double family_ms[FamilyCount] = {};
     int64_t family_launches[FamilyCount] = {};
-    int64_t launches = 0;
+    int64_t launches = 0, graph_launches = 0;
+    cudaGraphExec_t step_graph = nullptr; // one captured training step
+    bool graph_warm = false;
+    uint64_t graph_generation = 0;
+    void drop_graph();
 
     explicit Engine(const TgConfigEx &c);
     ~Engine();

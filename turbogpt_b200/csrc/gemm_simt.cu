@@ -23,13 +23,13 @@ template <class Out> struct EpilogueOps {
         }
         case Epilogue::GeluDual: {
             float pre = rounded<Out>(value);
-            c[c_index] = from_float<Out>(pre);
+            c[c_index] = from_float<Out>(gelu_derivative(pre));
             ((Out *)g.c2 + z * g.c_batch)[c_index] = from_float<Out>(gelu(pre));
             break;
         }
         case Epilogue::GeluGrad: {
             const Out *r = (const Out *)g.r + z * g.r_batch;
-            c[c_index] = from_float<Out>(rounded<Out>(value) * gelu_derivative(to_float(r[r_index])));
+            c[c_index] = from_float<Out>(rounded<Out>(value) * to_float(r[r_index]));
             break;
         }
         case Epilogue::Axpby: {

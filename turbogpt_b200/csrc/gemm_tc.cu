@@ -23,6 +23,7 @@
 #include "device_utils.cuh"
 #include "sm100.cuh"
 #include <cstdlib>
+#include <atomic>
 #include <mutex>
 #include <type_traits>
 #include <unordered_map>
@@ -71,16 +72,6 @@ __device__ __forceinline__ void gelu_terms(float x, float &cdf, float &density) 
     const float tail = poly * t * e;
     cdf = x >= 0.f ? 1.f - tail : tail;
     density = 0.3989422804014327f * e; // exp(-x^2/2) / sqrt(2 pi)
-}
-__device__ __forceinline__ float fast_gelu(float x) {
-    float cdf, density;
-    gelu_terms(x, cdf, density);
-    return x * cdf;
-}
-__device__ __forceinline__ float fast_gelu_derivative(float x) {
-    float cdf, density;
-    gelu_terms(x, cdf, density);
-    return fmaf(x, density, cdf);
 }
 
 // Direct global store of eight consecutive outputs (split-K reduction path only).
@@ -409,17 +400,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                             } else if constexpr (Kind == int(Epilogue::GeluDual)) {
                                 uint32_t activated[8];
 #pragma unroll
-                                for (int j = 0; j < 16; ++j)
-                                    v[j] = rounded<bf16>(v[j]);
-#pragma unroll
-                                for (int j = 0; j < 8; ++j)
-                                    activated[j] = pack_bf16(fast_gelu(v[2 * j]), fast_gelu(v[2 * j + 1]));
+                                for (int j = 0; j < 8; ++j) { // v becomes gelu'(pre), `activated` gelu(pre)
+                                    float cdf0, cdf1, den0, den1;
+                                    const float x0 = rounded<bf16>(v[2 * j]), x1 = rounded<bf16>(v[2 * j + 1]);
+                                    gelu_terms(x0, cdf0, den0);
+                                    gelu_terms(x1, cdf1, den1);
+                                    activated[j] = pack_bf16(x0 * cdf0, x1 * cdf1);
+                                    v[2 * j] = fmaf(x0, den0, cdf0);
+                                    v[2 * j + 1] = fmaf(x1, den1, cdf1);
+                                }
                                 store_global32((char *)p.c2 + (c_row + column) * 2 + g * 32, activated, whole,
                                                column + g * 16 + 8 < p.n);
                             } else if constexpr (Kind == int(Epilogue::GeluGrad)) {
 #pragma unroll
                                 for (int j = 0; j < 16; ++j)
-                                    v[j] = rounded<bf16>(v[j]) * fast_gelu_derivative(r[j]);
+                                    v[j] = rounded<bf16>(v[j]) * r[j];
                             } else if constexpr (Kind == int(Epilogue::Axpby)) {
 #pragma unroll
                                 for (int j = 0; j < 16; ++j)
@@ -544,6 +539,7 @@ struct Workspace {
 };
 std::mutex workspace_mutex;
 std::unordered_map<int, Workspace> workspaces; // per device
+std::atomic<uint64_t> workspace_generation{1};
 
 // Split-K workspace, grown on demand outside stream capture; one per device, shared by the
 // engine's single stream.
@@ -557,6 +553,7 @@ Workspace &workspace_for(size_t partial_bytes, size_t tickets, cudaStream_t s) {
         if (w.partials)
             CHECK_CUDA(cudaFree(w.partials));
         CHECK_CUDA(cudaMalloc(&w.partials, partial_bytes));
+        ++workspace_generation;
         w.partial_bytes = partial_bytes;
     }
     if (w.ticket_count < tickets) {
@@ -565,6 +562,7 @@ Workspace &workspace_for(size_t partial_bytes, size_t tickets, cudaStream_t s) {
             CHECK_CUDA(cudaFree(w.tickets));
         CHECK_CUDA(cudaMalloc(&w.tickets, tickets * sizeof(unsigned)));
         CHECK_CUDA(cudaMemset(w.tickets, 0, tickets * sizeof(unsigned)));
+        ++workspace_generation;
         w.ticket_count = tickets;
     }
     return w;
@@ -572,6 +570,7 @@ Workspace &workspace_for(size_t partial_bytes, size_t tickets, cudaStream_t s) {
 } // namespace
 
 int gemm_tc_shared_bytes() { return MaxShared; }
+uint64_t gemm_tc_workspace_generation() { return workspace_generation.load(); }
 
 bool gemm_tc_supported(const GemmArgs &g) {
     if (g.in != Dtype::BF16)

@@ -142,8 +142,8 @@ void launch_loss_history(const float *token_losses, float *history, const StepCo
 enum class Epilogue {
     Store = 0,     // C = acc
     Residual = 1,  // C = round(acc) + R            (reference cuda/mma.cuh:96-99)
-    GeluDual = 2,  // C = round(acc); C2 = gelu(C)
-    GeluGrad = 3,  // C = acc * gelu'(R)
+    GeluDual = 2,  // pre = round(acc); C = gelu'(pre) (kept for backward); C2 = gelu(pre)
+    GeluGrad = 3,  // C = round(acc) * R, R = the saved gelu'(pre)
     Axpby = 4,     // C = alpha * acc + beta * R    (Newton-Schulz updates)
 };
 struct GemmArgs {
@@ -168,6 +168,7 @@ void launch_gemm_simt(const GemmArgs &g, cudaStream_t s);
 bool gemm_tc_supported(const GemmArgs &g);
 void launch_gemm_tc(const GemmArgs &g, int sms, StepCounters *counters, cudaStream_t s);
 int gemm_tc_shared_bytes();
+uint64_t gemm_tc_workspace_generation(); // bumped whenever the split-K workspace is reallocated
 // Weight gradient dW[out, in] = dy^T x whose split-K scratch is a fixed array inside the library:
 // allocates nothing (see gemm_tc.cu).  Throws when the shape needs more scratch than the array holds.
 void launch_weight_gradient_static(const void *dy, const void *x, float *dw, int out, int in, int tokens, int sms,
