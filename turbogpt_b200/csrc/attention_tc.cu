@@ -270,19 +270,26 @@ flash_forward_kernel(const __grid_constant__ CUtensorMap map_qkv, ForwardParams 
 
 // ------------------------------------------------------------------------------------------
 // Backward.  Two kernels, both deterministic (no atomics):
-//   dq kernel    : one CTA per 128 query rows, loops over key blocks of 64.  S = Q K^T and
+//   dq kernel    : one CTA per 128 query rows, stepping over keys 32 at a time.  S = Q K^T and
 //                  dP = dO V^T land in tensor memory; thread = query row computes
-//                  dS = P (dP - delta) / sqrt(d) with P = exp(S / sqrt(d) - lse), packs it to BF16 in
-//                  tensor memory, and dQ += dS K accumulates in tensor memory across the loop.
-//   dk/dv kernel : one CTA per 128 keys, loops over query blocks of 64 with everything
+//                  dS = P (dP - delta) with P = exp(S / sqrt(d) - lse), packs it to BF16 over S,
+//                  and dQ += dS K accumulates in tensor memory; 1 / sqrt(d) is applied once at the end.
+//   dk/dv kernel : one CTA per 128 keys, stepping over queries 32 at a time with everything
 //                  transposed (S^T = K Q^T, dP^T = V dO^T: thread = key row), so P^T and dS^T are
 //                  A operands in tensor memory for dV += P^T dO and dK += dS^T Q.
-// Both keep 256 TMEM columns and under 100 KB of shared memory, so two CTAs share an SM.
+// Both are software pipelines: the score buffers are ring-buffered in tensor memory (three deep in
+// the dq kernel, two in the dk/dv kernel), and the MMA thread issues the score products two steps
+// ahead of the accumulation products, so the tensor pipe works on steps j-1 and j+1 while the
+// compute warps turn step j's scores into dS.  256 TMEM columns and under 80 KB of shared memory
+// per CTA: two CTAs share an SM.
 // ------------------------------------------------------------------------------------------
-constexpr int BackwardThreads = 320, BackwardTmemColumns = 256, // warp 0 TMA, warp 1 MMA, 8 compute warps
-               HalfTileBytes = 64 * HeadSize * 2; // 8 KB
-constexpr int DqShared = 2 * TileBytes + 4 * HalfTileBytes + 1024 + 256;      // Q, dO + 2 x (K, V) blocks
-constexpr int DkvShared = 2 * TileBytes + 4 * HalfTileBytes + 1024 + 1024 + 256; // K, V + 2 x (Q, dO) + statistics
+constexpr int BackwardThreads = 320, BackwardTmemColumns = 256; // warp 0 TMA, warp 1 MMA, 8 compute warps
+constexpr int Step = 32;                                        // keys (dq) or queries (dk/dv) per pipeline step
+constexpr int StepBytes = Step * HeadSize * 2;                  // 4 KB: one K, V, Q or dO block
+constexpr int Ring = 4;                                         // shared-memory ring of operand blocks
+constexpr int DqStages = 3, DkvStages = 2;                      // score buffers in tensor memory
+constexpr int DqShared = 2 * TileBytes + Ring * 2 * StepBytes + 1024 + 256; // Q, dO + ring of (K, V)
+constexpr int DkvShared = 2 * TileBytes + Ring * 2 * StepBytes + Ring * 64 * 4 + 1024 + 256; // + statistics
 
 struct BackwardParams {
     bf16 *dqkv;
@@ -292,21 +299,34 @@ struct BackwardParams {
     StepCounters *counters;
 };
 
-__device__ __forceinline__ void load_columns_64(uint32_t address, uint32_t (&a)[32], uint32_t (&b)[32]) {
+// Eight accumulator rows x 32 columns from tensor memory, scaled, to BF16 in global memory.
+__device__ __forceinline__ void store_accumulator(uint32_t address, bf16 *out, float factor, bool write) {
+    uint32_t a[32];
     tmem_load_32x32_async(address, a);
-    tmem_load_32x32_async(address + 32, b);
+    tmem_wait_load(a);
+    if (write) {
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+            float v[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+                v[i] = __uint_as_float(a[g * 8 + i]) * factor;
+            store8(out + g * 8, v);
+        }
+    }
 }
 
 __global__ void __launch_bounds__(BackwardThreads, 2)
-flash_dq_kernel(const __grid_constant__ CUtensorMap map_qkv128, const __grid_constant__ CUtensorMap map_qkv64,
+flash_dq_kernel(const __grid_constant__ CUtensorMap map_qkv128, const __grid_constant__ CUtensorMap map_qkv32,
                 const __grid_constant__ CUtensorMap map_do128, BackwardParams p) {
     extern __shared__ uint8_t raw_shared[];
     const uint32_t base = (smem_address(raw_shared) + 1023u) & ~1023u;
     uint8_t *aligned = raw_shared + (base - smem_address(raw_shared));
-    uint64_t *barriers = reinterpret_cast<uint64_t *>(aligned + 2 * TileBytes + 4 * HalfTileBytes);
-    const uint32_t qdo_full = smem_address(barriers), kv_full0 = qdo_full + 8, kv_empty0 = kv_full0 + 16,
-                   s_full = kv_empty0 + 16, ds_full = s_full + 8, dq_done = ds_full + 8;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(barriers + 8);
+    uint64_t *barriers = reinterpret_cast<uint64_t *>(aligned + 2 * TileBytes + Ring * 2 * StepBytes);
+    const uint32_t qdo_full = smem_address(barriers), kv_full0 = qdo_full + 8, kv_empty0 = kv_full0 + 8 * Ring,
+                   s_full0 = kv_empty0 + 8 * Ring, ds_full0 = s_full0 + 8 * DqStages,
+                   dq_done = ds_full0 + 8 * DqStages; // 2 + 2 Ring + 2 DqStages = 16 barriers
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(barriers + 2 + 2 * Ring + 2 * DqStages);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
     const uint32_t smem_q = base, smem_do = base + TileBytes, smem_kv = base + 2 * TileBytes;
 
@@ -316,16 +336,18 @@ flash_dq_kernel(const __grid_constant__ CUtensorMap map_qkv128, const __grid_con
     const int bh = blockIdx.x % pairs, b = bh / p.heads, h = bh % p.heads;
     const int row0 = b * p.context;
     const int last_key = min(p.context, (tile + 1) * BlockM); // keys 0..last_key-1 can be attended
-    const int blocks = (last_key + 63) / 64;
+    const int blocks = (last_key + Step - 1) / Step;
 
     if (threadIdx.x == 0) {
         mbarrier_init(qdo_full, 1);
-        for (int s = 0; s < 2; ++s) {
+        for (int s = 0; s < Ring; ++s) {
             mbarrier_init(kv_full0 + 8 * s, 1);
             mbarrier_init(kv_empty0 + 8 * s, 1);
         }
-        mbarrier_init(s_full, 1);
-        mbarrier_init(ds_full, 8);
+        for (int s = 0; s < DqStages; ++s) {
+            mbarrier_init(s_full0 + 8 * s, 1);
+            mbarrier_init(ds_full0 + 8 * s, 8);
+        }
         mbarrier_init(dq_done, 1);
         *abort_flag = 0;
         fence_barrier_init();
@@ -338,7 +360,8 @@ flash_dq_kernel(const __grid_constant__ CUtensorMap map_qkv128, const __grid_con
     __syncthreads();
     tcgen05_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    const uint32_t tmem_s = tmem_base, tmem_dp = tmem_base + 64, tmem_dq = tmem_base + 128; // dS packs into S
+    // stage s: S at 64 s (dS packs into columns 0-7 and 16-23 of it), dP at 64 s + 32; dQ at 192
+    const uint32_t tmem_dq = tmem_base + 64 * DqStages;
 
     if (warp == 0) {
         if (elect_one()) {
@@ -346,108 +369,131 @@ flash_dq_kernel(const __grid_constant__ CUtensorMap map_qkv128, const __grid_con
             tma_load_3d(smem_q, &map_qkv128, h * HeadSize, row0 + tile * BlockM, 0, qdo_full);
             tma_load_3d(smem_do, &map_do128, h * HeadSize, row0 + tile * BlockM, 0, qdo_full);
             for (int j = 0; j < blocks; ++j) {
-                const int stage = j & 1;
-                if (!mbarrier_wait(kv_empty0 + 8 * stage, ((j >> 1) & 1) ^ 1, abort_flag, p.counters, 301))
+                const int ring = j % Ring;
+                if (!mbarrier_wait(kv_empty0 + 8 * ring, ((j / Ring) & 1) ^ 1, abort_flag, p.counters, 301))
                     break;
-                const uint32_t bar = kv_full0 + 8 * stage, dst = smem_kv + stage * 2 * HalfTileBytes;
-                mbarrier_expect_tx(bar, 2 * HalfTileBytes);
-                tma_load_3d(dst, &map_qkv64, p.width + h * HeadSize, row0 + j * 64, 0, bar);
-                tma_load_3d(dst + HalfTileBytes, &map_qkv64, 2 * p.width + h * HeadSize, row0 + j * 64, 0, bar);
+                const uint32_t bar = kv_full0 + 8 * ring, dst = smem_kv + ring * 2 * StepBytes;
+                mbarrier_expect_tx(bar, 2 * StepBytes);
+                tma_load_3d(dst, &map_qkv32, p.width + h * HeadSize, row0 + j * Step, 0, bar);
+                tma_load_3d(dst + StepBytes, &map_qkv32, 2 * p.width + h * HeadSize, row0 + j * Step, 0, bar);
             }
         }
     } else if (warp == 1) {
         if (elect_one()) {
-            const uint32_t idesc_s = instruction_descriptor(BlockM, 64, 0, 0);
+            const uint32_t idesc_s = instruction_descriptor(BlockM, Step, 0, 0);
             const uint32_t idesc_dq = instruction_descriptor(BlockM, HeadSize, 0, 1);
             bool ok = mbarrier_wait(qdo_full, 0, abort_flag, p.counters, 302);
-            for (int j = 0; j < blocks && ok; ++j) {
-                const uint32_t k_tile = smem_kv + (j & 1) * 2 * HalfTileBytes, v_tile = k_tile + HalfTileBytes;
-                ok = mbarrier_wait(kv_full0 + 8 * (j & 1), (j >> 1) & 1, abort_flag, p.counters, 303);
+            int issued = 0, stage_in = 0; // score products issued so far, and the stage the next one fills
+            auto issue_scores = [&]() {
+                const int ring = issued % Ring;
+                const uint32_t k_tile = smem_kv + ring * 2 * StepBytes, v_tile = k_tile + StepBytes;
+                ok = mbarrier_wait(kv_full0 + 8 * ring, (issued / Ring) & 1, abort_flag, p.counters, 303);
                 if (!ok)
-                    break;
+                    return;
                 tcgen05_fence_after();
+                const uint32_t t = tmem_base + 64 * stage_in;
 #pragma unroll
                 for (int ks = 0; ks < HeadSize / 16; ++ks)
-                    tcgen05_mma_bf16(tmem_s, smem_descriptor(smem_q + ks * 32, 16, 1024),
+                    tcgen05_mma_bf16(t, smem_descriptor(smem_q + ks * 32, 16, 1024),
                                      smem_descriptor(k_tile + ks * 32, 16, 1024), idesc_s, ks > 0);
 #pragma unroll
                 for (int ks = 0; ks < HeadSize / 16; ++ks)
-                    tcgen05_mma_bf16(tmem_dp, smem_descriptor(smem_do + ks * 32, 16, 1024),
+                    tcgen05_mma_bf16(t + 32, smem_descriptor(smem_do + ks * 32, 16, 1024),
                                      smem_descriptor(v_tile + ks * 32, 16, 1024), idesc_s, ks > 0);
-                tcgen05_commit(s_full);
-                ok = mbarrier_wait(ds_full, j & 1, abort_flag, p.counters, 304);
+                tcgen05_commit(s_full0 + 8 * stage_in);
+                ++issued;
+                stage_in = stage_in + 1 == DqStages ? 0 : stage_in + 1;
+            };
+            if (ok)
+                issue_scores();
+            if (ok && blocks > 1)
+                issue_scores();
+            int stage = 0, phase = 0;
+            for (int j = 0; j < blocks && ok; ++j) {
+                ok = mbarrier_wait(ds_full0 + 8 * stage, phase, abort_flag, p.counters, 304);
                 if (!ok)
                     break;
                 tcgen05_fence_after();
+                const int ring = j % Ring;
+                const uint32_t k_tile = smem_kv + ring * 2 * StepBytes;
 #pragma unroll
-                for (int ks = 0; ks < 64 / 16; ++ks) // dQ += dS K_j: four 16-key steps (dS: columns 0-15 and 32-47)
-                    tcgen05_mma_bf16_ts(tmem_dq, tmem_s + (ks / 2) * 32 + (ks % 2) * 8,
-                                        smem_descriptor(k_tile + ks * 2048, 8192, 1024),
-                                        idesc_dq, (j > 0 || ks > 0) ? 1u : 0u);
-                tcgen05_commit(kv_empty0 + 8 * (j & 1));
+                for (int ks = 0; ks < Step / 16; ++ks) // dQ += dS K_j: 16 keys (8 packed columns at 16 ks) at a time
+                    tcgen05_mma_bf16_ts(tmem_dq, tmem_base + 64 * stage + ks * 16,
+                                        smem_descriptor(k_tile + ks * 2048, 8192, 1024), idesc_dq,
+                                        (j > 0 || ks > 0) ? 1u : 0u);
+                tcgen05_commit(kv_empty0 + 8 * ring);
+                if (issued < blocks)
+                    issue_scores(); // reuses the stage whose dS the MMAs issued one step ago have read
+                if (++stage == DqStages)
+                    stage = 0, phase ^= 1;
             }
             if (ok)
                 tcgen05_commit(dq_done);
         }
     } else {
-        // Two warps share each 32-lane quarter: warp `half` takes score columns half*32 .. half*32+31
-        // and leaves its 16 packed dS columns at the start of its own column range.
+        // Two warps share each 32-lane quarter: warp `half` takes 16 of the step's 32 keys and leaves
+        // its 8 packed dS columns at the start of its own 16 score columns (the other warp may still
+        // be reading its own).
         const int quarter = warp % 4, half = (warp - 2) / 4;
         const int row = quarter * 32 + lane, position = tile * BlockM + row;
-        const uint32_t lane_base = (uint32_t(quarter * 32) << 16) + half * 32;
-        const bool valid = position < p.context;
+        const int warp_first = tile * BlockM + quarter * 32; // earliest query of this warp
+        const uint32_t lane_base = tmem_base + (uint32_t(quarter * 32) << 16);
+        const bool valid = position < p.context, ragged = warp_first + 31 >= p.context;
         const int64_t stat = (int64_t(b) * p.heads + h) * p.context + position;
         const float lse2 = valid ? p.lse[stat] * 1.4426950408889634f : 0.f;
         const float delta = valid ? p.delta[stat] : 0.f;
         bool ok = true;
+        int stage = 0, phase = 0;
         for (int j = 0; j < blocks; ++j) {
-            ok = mbarrier_wait(s_full, j & 1, abort_flag, p.counters, 305);
+            ok = mbarrier_wait(s_full0 + 8 * stage, phase, abort_flag, p.counters, 305);
             if (!ok)
                 break;
             tcgen05_fence_after();
-            uint32_t sc[32], dp[32], packed[16];
-            tmem_load_32x32_async(tmem_s + lane_base, sc);
-            tmem_load_32x32_async(tmem_dp + lane_base, dp);
+            uint32_t sc[16], dp[16], packed[8];
+            const uint32_t t = lane_base + 64 * stage;
+            tmem_load_32x16_async(t + half * 16, sc);
+            tmem_load_32x16_async(t + 32 + half * 16, dp);
             tmem_wait_load(sc);
             tmem_wait_load(dp);
-            const int key0 = j * 64 + half * 32;
-            const bool masked_block = key0 + 32 > position; // some keys of this range lie after the query
+            const int key0 = j * Step + half * 16;
+            if (key0 + 15 > warp_first || ragged) { // the causal diagonal crosses this warp's block
 #pragma unroll
-            for (int i = 0; i < 32; i += 2) {
-                float v[2];
+                for (int i = 0; i < 16; i += 2) {
+                    float v[2];
 #pragma unroll
-                for (int u = 0; u < 2; ++u) {
-                    float prob = fast_exp2(fmaf(__uint_as_float(sc[i + u]), p.scale_log2, -lse2));
-                    float ds = prob * (__uint_as_float(dp[i + u]) - delta) * p.scale;
-                    v[u] = (masked_block && key0 + i + u > position) || !valid ? 0.f : ds;
+                    for (int u = 0; u < 2; ++u) {
+                        float prob = fast_exp2(fmaf(__uint_as_float(sc[i + u]), p.scale_log2, -lse2));
+                        float ds = prob * (__uint_as_float(dp[i + u]) - delta);
+                        v[u] = key0 + i + u > position || !valid ? 0.f : ds;
+                    }
+                    packed[i / 2] = pack_bf16(v[0], v[1]);
                 }
-                packed[i / 2] = pack_bf16(v[0], v[1]);
+            } else {
+#pragma unroll
+                for (int i = 0; i < 16; i += 2) {
+                    float v[2];
+#pragma unroll
+                    for (int u = 0; u < 2; ++u)
+                        v[u] = fast_exp2(fmaf(__uint_as_float(sc[i + u]), p.scale_log2, -lse2)) *
+                               (__uint_as_float(dp[i + u]) - delta);
+                    packed[i / 2] = pack_bf16(v[0], v[1]);
+                }
             }
-            tmem_store_32x16(tmem_s + lane_base, packed);
+            tmem_store_32x8(t + half * 16, packed);
             tmem_wait_store();
             tcgen05_fence_before();
             __syncwarp();
             if (lane == 0)
-                mbarrier_arrive(ds_full);
+                mbarrier_arrive(ds_full0 + 8 * stage);
+            if (++stage == DqStages)
+                stage = 0, phase ^= 1;
         }
         if (ok)
             ok = mbarrier_wait(dq_done, 0, abort_flag, p.counters, 306);
         if (ok) {
             tcgen05_fence_after();
-            uint32_t a[32];
-            tmem_load_32x32_async(tmem_dq + lane_base, a);
-            tmem_wait_load(a);
-            if (valid) {
-                bf16 *out = p.dqkv + (int64_t(row0) + position) * 3 * p.width + h * HeadSize + half * 32;
-#pragma unroll
-                for (int g = 0; g < 4; ++g) {
-                    float v[8];
-#pragma unroll
-                    for (int i = 0; i < 8; ++i)
-                        v[i] = __uint_as_float(a[g * 8 + i]);
-                    store8(out + g * 8, v);
-                }
-            }
+            bf16 *out = p.dqkv + (int64_t(row0) + position) * 3 * p.width + h * HeadSize + half * 32;
+            store_accumulator(tmem_dq + (uint32_t(quarter * 32) << 16) + half * 32, out, p.scale, valid);
         }
     }
     __syncthreads();
@@ -460,16 +506,18 @@ flash_dq_kernel(const __grid_constant__ CUtensorMap map_qkv128, const __grid_con
 }
 
 __global__ void __launch_bounds__(BackwardThreads, 2)
-flash_dkv_kernel(const __grid_constant__ CUtensorMap map_qkv128, const __grid_constant__ CUtensorMap map_qkv64,
-                 const __grid_constant__ CUtensorMap map_do64, BackwardParams p) {
+flash_dkv_kernel(const __grid_constant__ CUtensorMap map_qkv128, const __grid_constant__ CUtensorMap map_qkv32,
+                 const __grid_constant__ CUtensorMap map_do32, BackwardParams p) {
     extern __shared__ uint8_t raw_shared[];
     const uint32_t base = (smem_address(raw_shared) + 1023u) & ~1023u;
     uint8_t *aligned = raw_shared + (base - smem_address(raw_shared));
-    float *statistics = reinterpret_cast<float *>(aligned + 2 * TileBytes + 4 * HalfTileBytes); // [2][lse 64 | delta 64]
-    uint64_t *barriers = reinterpret_cast<uint64_t *>(aligned + 2 * TileBytes + 4 * HalfTileBytes + 1024);
-    const uint32_t kv_full = smem_address(barriers), qdo_full0 = kv_full + 8, qdo_empty0 = qdo_full0 + 16,
-                   s_full = qdo_empty0 + 16, pd_full = s_full + 8, acc_done = pd_full + 8;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(barriers + 8);
+    // per ring slot: lse (in base 2) of the step's 32 queries, then their delta
+    float *statistics = reinterpret_cast<float *>(aligned + 2 * TileBytes + Ring * 2 * StepBytes);
+    uint64_t *barriers = reinterpret_cast<uint64_t *>(aligned + 2 * TileBytes + Ring * 2 * StepBytes + Ring * 64 * 4);
+    const uint32_t kv_full = smem_address(barriers), qdo_full0 = kv_full + 8, qdo_empty0 = qdo_full0 + 8 * Ring,
+                   s_full0 = qdo_empty0 + 8 * Ring, pd_full0 = s_full0 + 8 * DkvStages,
+                   acc_done = pd_full0 + 8 * DkvStages; // 2 + 2 Ring + 2 DkvStages = 14 barriers
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(barriers + 2 + 2 * Ring + 2 * DkvStages);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
     const uint32_t smem_k = base, smem_v = base + TileBytes, smem_qdo = base + 2 * TileBytes;
 
@@ -478,17 +526,19 @@ flash_dkv_kernel(const __grid_constant__ CUtensorMap map_qkv128, const __grid_co
     const int tile = int(blockIdx.x / pairs); // key tile; early tiles have the most query blocks
     const int bh = blockIdx.x % pairs, b = bh / p.heads, h = bh % p.heads;
     const int row0 = b * p.context;
-    const int first_block = tile * 2, query_blocks = (p.context + 63) / 64; // query blocks first_block .. query_blocks-1
-    const int blocks = query_blocks - first_block;
+    const int first_block = tile * (BlockN / Step), query_blocks = (p.context + Step - 1) / Step;
+    const int blocks = query_blocks - first_block; // query blocks first_block .. query_blocks-1
 
     if (threadIdx.x == 0) {
         mbarrier_init(kv_full, 1);
-        for (int s = 0; s < 2; ++s) {
+        for (int s = 0; s < Ring; ++s) {
             mbarrier_init(qdo_full0 + 8 * s, 1);
             mbarrier_init(qdo_empty0 + 8 * s, 1);
         }
-        mbarrier_init(s_full, 1);
-        mbarrier_init(pd_full, 8);
+        for (int s = 0; s < DkvStages; ++s) {
+            mbarrier_init(s_full0 + 8 * s, 1);
+            mbarrier_init(pd_full0 + 8 * s, 8);
+        }
         mbarrier_init(acc_done, 1);
         *abort_flag = 0;
         fence_barrier_init();
@@ -501,148 +551,166 @@ flash_dkv_kernel(const __grid_constant__ CUtensorMap map_qkv128, const __grid_co
     __syncthreads();
     tcgen05_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    // S^T 0..63 (P^T packs into 0..31) | dP^T 64..127 (dS^T packs into 64..95) | dV 128..191 | dK 192..255
-    const uint32_t tmem_s = tmem_base, tmem_dp = tmem_base + 64, tmem_dv = tmem_base + 128, tmem_dk = tmem_base + 192;
+    // stage s: S^T at 64 s (P^T packs into columns 0-7 and 16-23 of it), dP^T at 64 s + 32 (dS^T packs
+    // likewise); dV at 128, dK at 192
+    const uint32_t tmem_dv = tmem_base + 64 * DkvStages, tmem_dk = tmem_dv + HeadSize;
 
     if (warp == 0) {
-        if (elect_one()) {
+        // The whole warp runs the producer loop: lane 0 issues the TMA loads, every lane fetches one
+        // query's statistics into the ring slot before lane 0's arrival releases them.
+        if (lane == 0) {
             mbarrier_expect_tx(kv_full, 2 * TileBytes);
             tma_load_3d(smem_k, &map_qkv128, p.width + h * HeadSize, row0 + tile * BlockN, 0, kv_full);
             tma_load_3d(smem_v, &map_qkv128, 2 * p.width + h * HeadSize, row0 + tile * BlockN, 0, kv_full);
-            for (int i = 0; i < blocks; ++i) {
-                const int stage = i & 1;
-                if (!mbarrier_wait(qdo_empty0 + 8 * stage, ((i >> 1) & 1) ^ 1, abort_flag, p.counters, 311))
-                    break;
-                const uint32_t bar = qdo_full0 + 8 * stage, dst = smem_qdo + stage * 2 * HalfTileBytes;
-                mbarrier_expect_tx(bar, 2 * HalfTileBytes);
-                tma_load_3d(dst, &map_qkv64, h * HeadSize, row0 + (first_block + i) * 64, 0, bar);
-                tma_load_3d(dst + HalfTileBytes, &map_do64, h * HeadSize, row0 + (first_block + i) * 64, 0, bar);
+        }
+        const float *lse = p.lse + (int64_t(b) * p.heads + h) * p.context;
+        const float *delta = p.delta + (int64_t(b) * p.heads + h) * p.context;
+        for (int i = 0; i < blocks; ++i) {
+            const int ring = i % Ring, q = (first_block + i) * Step + lane;
+            float lse2 = 0.f, dl = 0.f;
+            if (q < p.context) {
+                lse2 = lse[q] * 1.4426950408889634f;
+                dl = delta[q];
+            }
+            bool ok = mbarrier_wait(qdo_empty0 + 8 * ring, ((i / Ring) & 1) ^ 1, abort_flag, p.counters, 311);
+            if (!__all_sync(0xffffffffu, ok))
+                break;
+            statistics[ring * 64 + lane] = lse2;
+            statistics[ring * 64 + 32 + lane] = dl;
+            __syncwarp();
+            if (lane == 0) {
+                const uint32_t bar = qdo_full0 + 8 * ring, dst = smem_qdo + ring * 2 * StepBytes;
+                mbarrier_expect_tx(bar, 2 * StepBytes);
+                tma_load_3d(dst, &map_qkv32, h * HeadSize, row0 + (first_block + i) * Step, 0, bar);
+                tma_load_3d(dst + StepBytes, &map_do32, h * HeadSize, row0 + (first_block + i) * Step, 0, bar);
             }
         }
     } else if (warp == 1) {
         if (elect_one()) {
-            const uint32_t idesc_s = instruction_descriptor(BlockN, 64, 0, 0);
+            const uint32_t idesc_s = instruction_descriptor(BlockN, Step, 0, 0);
             const uint32_t idesc_acc = instruction_descriptor(BlockN, HeadSize, 0, 1);
             bool ok = mbarrier_wait(kv_full, 0, abort_flag, p.counters, 312);
-            for (int i = 0; i < blocks && ok; ++i) {
-                const uint32_t q_tile = smem_qdo + (i & 1) * 2 * HalfTileBytes, do_tile = q_tile + HalfTileBytes;
-                ok = mbarrier_wait(qdo_full0 + 8 * (i & 1), (i >> 1) & 1, abort_flag, p.counters, 313);
+            int issued = 0;
+            auto issue_scores = [&]() {
+                const int ring = issued % Ring;
+                const uint32_t q_tile = smem_qdo + ring * 2 * StepBytes, do_tile = q_tile + StepBytes;
+                ok = mbarrier_wait(qdo_full0 + 8 * ring, (issued / Ring) & 1, abort_flag, p.counters, 313);
                 if (!ok)
-                    break;
+                    return;
                 tcgen05_fence_after();
+                const uint32_t t = tmem_base + 64 * (issued % DkvStages);
 #pragma unroll
                 for (int ks = 0; ks < HeadSize / 16; ++ks) // S^T = K Q_i^T
-                    tcgen05_mma_bf16(tmem_s, smem_descriptor(smem_k + ks * 32, 16, 1024),
+                    tcgen05_mma_bf16(t, smem_descriptor(smem_k + ks * 32, 16, 1024),
                                      smem_descriptor(q_tile + ks * 32, 16, 1024), idesc_s, ks > 0);
 #pragma unroll
                 for (int ks = 0; ks < HeadSize / 16; ++ks) // dP^T = V dO_i^T
-                    tcgen05_mma_bf16(tmem_dp, smem_descriptor(smem_v + ks * 32, 16, 1024),
+                    tcgen05_mma_bf16(t + 32, smem_descriptor(smem_v + ks * 32, 16, 1024),
                                      smem_descriptor(do_tile + ks * 32, 16, 1024), idesc_s, ks > 0);
-                tcgen05_commit(s_full);
-                ok = mbarrier_wait(pd_full, i & 1, abort_flag, p.counters, 314);
+                tcgen05_commit(s_full0 + 8 * (issued % DkvStages));
+                ++issued;
+            };
+            if (ok)
+                issue_scores();
+            if (ok && blocks > 1)
+                issue_scores();
+            for (int i = 0; i < blocks && ok; ++i) {
+                const int stage = i % DkvStages, ring = i % Ring;
+                ok = mbarrier_wait(pd_full0 + 8 * stage, (i / DkvStages) & 1, abort_flag, p.counters, 314);
                 if (!ok)
                     break;
                 tcgen05_fence_after();
+                const uint32_t q_tile = smem_qdo + ring * 2 * StepBytes, do_tile = q_tile + StepBytes;
+                const uint32_t t = tmem_base + 64 * stage;
 #pragma unroll
-                for (int ks = 0; ks < 64 / 16; ++ks) // dV += P^T dO_i
-                    tcgen05_mma_bf16_ts(tmem_dv, tmem_s + (ks / 2) * 32 + (ks % 2) * 8,
-                                        smem_descriptor(do_tile + ks * 2048, 8192, 1024),
+                for (int ks = 0; ks < Step / 16; ++ks) // dV += P^T dO_i
+                    tcgen05_mma_bf16_ts(tmem_dv, t + ks * 16, smem_descriptor(do_tile + ks * 2048, 8192, 1024),
                                         idesc_acc, (i > 0 || ks > 0) ? 1u : 0u);
 #pragma unroll
-                for (int ks = 0; ks < 64 / 16; ++ks) // dK += dS^T Q_i
-                    tcgen05_mma_bf16_ts(tmem_dk, tmem_dp + (ks / 2) * 32 + (ks % 2) * 8,
-                                        smem_descriptor(q_tile + ks * 2048, 8192, 1024),
+                for (int ks = 0; ks < Step / 16; ++ks) // dK += dS^T Q_i
+                    tcgen05_mma_bf16_ts(tmem_dk, t + 32 + ks * 16, smem_descriptor(q_tile + ks * 2048, 8192, 1024),
                                         idesc_acc, (i > 0 || ks > 0) ? 1u : 0u);
-                tcgen05_commit(qdo_empty0 + 8 * (i & 1));
+                tcgen05_commit(qdo_empty0 + 8 * ring);
+                if (issued < blocks)
+                    issue_scores(); // into the stage the products above have just read
             }
             if (ok)
                 tcgen05_commit(acc_done);
         }
     } else {
-        // Two warps share each 32-lane quarter and take 32 of the 64 query columns each; their packed
-        // P^T / dS^T columns sit at the start of their own column range (0-15 and 32-47).
+        // Two warps share each 32-lane quarter and take 16 of the step's 32 queries each; their packed
+        // P^T / dS^T columns sit at the start of their own 16 columns.
         const int quarter = warp % 4, half = (warp - 2) / 4;
         const int row = quarter * 32 + lane, key = tile * BlockN + row; // key position inside the sequence
-        const uint32_t lane_base = (uint32_t(quarter * 32) << 16) + half * 32;
-        const int t256 = threadIdx.x - 64; // 0..255 among the compute threads
-        const float *lse = p.lse + (int64_t(b) * p.heads + h) * p.context;
-        const float *delta = p.delta + (int64_t(b) * p.heads + h) * p.context;
+        const int warp_last = tile * BlockN + quarter * 32 + 31;        // latest key of this warp
+        const uint32_t lane_base = tmem_base + (uint32_t(quarter * 32) << 16);
         bool ok = true;
         for (int i = 0; i < blocks; ++i) {
-            const int q0 = (first_block + i) * 64;
-            float *stats = statistics + (i & 1) * 128;
-            if (t256 < 128) { // one statistic per thread: lse (scaled to base 2) for 64 queries, then delta
-                const int q = q0 + (t256 & 63);
-                float value = 0.f;
-                if (q < p.context)
-                    value = t256 < 64 ? lse[q] * 1.4426950408889634f : delta[q];
-                stats[t256] = value;
-            }
-            asm volatile("bar.sync 1, 256;" ::: "memory");
-            bool ready = mbarrier_wait(s_full, i & 1, abort_flag, p.counters, 315);
-            // all eight warps meet at the named barrier above every iteration: leave together
-            uint32_t all_ready;
-            asm volatile("{\n\t.reg .pred a, c;\n\tsetp.ne.u32 a, %1, 0;\n\tbar.red.and.pred c, 2, 256, a;\n\t"
-                         "selp.u32 %0, 1, 0, c;\n\t}"
-                         : "=r"(all_ready)
-                         : "r"(uint32_t(ready))
-                         : "memory");
-            ok = all_ready != 0;
+            const int stage = i % DkvStages, ring = i % Ring;
+            ok = mbarrier_wait(qdo_full0 + 8 * ring, (i / Ring) & 1, abort_flag, p.counters, 317) && // statistics
+                 mbarrier_wait(s_full0 + 8 * stage, (i / DkvStages) & 1, abort_flag, p.counters, 315);
             if (!ok)
                 break;
             tcgen05_fence_after();
-            uint32_t sc[32], dp[32], pp[16], pd[16];
-            tmem_load_32x32_async(tmem_s + lane_base, sc);
-            tmem_load_32x32_async(tmem_dp + lane_base, dp);
+            uint32_t sc[16], dp[16], pp[8], pd[8];
+            const uint32_t t = lane_base + 64 * stage + half * 16;
+            tmem_load_32x16_async(t, sc);
+            tmem_load_32x16_async(t + 32, dp);
+            float l2[16], dl[16];
+            const float4 *stats = reinterpret_cast<const float4 *>(statistics + ring * 64 + half * 16);
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const float4 a = stats[c], d = stats[8 + c];
+                l2[4 * c] = a.x, l2[4 * c + 1] = a.y, l2[4 * c + 2] = a.z, l2[4 * c + 3] = a.w;
+                dl[4 * c] = d.x, dl[4 * c + 1] = d.y, dl[4 * c + 2] = d.z, dl[4 * c + 3] = d.w;
+            }
             tmem_wait_load(sc);
             tmem_wait_load(dp);
-            const int qa = q0 + half * 32; // first query of this warp's columns
-            const bool edge = qa < key + 1 || qa + 32 > p.context; // causal diagonal or ragged end
+            const int qa = (first_block + i) * Step + half * 16; // first query of this warp's columns
+            if (qa < warp_last || qa + 16 > p.context) {         // causal diagonal or ragged end
 #pragma unroll
-            for (int c = 0; c < 32; c += 2) {
-                float pv[2], dv[2];
+                for (int c = 0; c < 16; c += 2) {
+                    float pv[2], dv[2];
 #pragma unroll
-                for (int u = 0; u < 2; ++u) {
-                    const int col = half * 32 + c + u;
-                    float prob = fast_exp2(fmaf(__uint_as_float(sc[c + u]), p.scale_log2, -stats[col]));
-                    if (edge && (q0 + col < key || q0 + col >= p.context))
-                        prob = 0.f;
-                    pv[u] = prob;
-                    dv[u] = prob * (__uint_as_float(dp[c + u]) - stats[64 + col]) * p.scale;
+                    for (int u = 0; u < 2; ++u) {
+                        float prob = fast_exp2(fmaf(__uint_as_float(sc[c + u]), p.scale_log2, -l2[c + u]));
+                        if (qa + c + u < key || qa + c + u >= p.context)
+                            prob = 0.f;
+                        pv[u] = prob;
+                        dv[u] = prob * (__uint_as_float(dp[c + u]) - dl[c + u]);
+                    }
+                    pp[c / 2] = pack_bf16(pv[0], pv[1]);
+                    pd[c / 2] = pack_bf16(dv[0], dv[1]);
                 }
-                pp[c / 2] = pack_bf16(pv[0], pv[1]);
-                pd[c / 2] = pack_bf16(dv[0], dv[1]);
+            } else {
+#pragma unroll
+                for (int c = 0; c < 16; c += 2) {
+                    float pv[2], dv[2];
+#pragma unroll
+                    for (int u = 0; u < 2; ++u) {
+                        pv[u] = fast_exp2(fmaf(__uint_as_float(sc[c + u]), p.scale_log2, -l2[c + u]));
+                        dv[u] = pv[u] * (__uint_as_float(dp[c + u]) - dl[c + u]);
+                    }
+                    pp[c / 2] = pack_bf16(pv[0], pv[1]);
+                    pd[c / 2] = pack_bf16(dv[0], dv[1]);
+                }
             }
-            tmem_store_32x16(tmem_s + lane_base, pp);
-            tmem_store_32x16(tmem_dp + lane_base, pd);
+            tmem_store_32x8(t, pp);
+            tmem_store_32x8(t + 32, pd);
             tmem_wait_store();
             tcgen05_fence_before();
             __syncwarp();
             if (lane == 0)
-                mbarrier_arrive(pd_full);
+                mbarrier_arrive(pd_full0 + 8 * stage);
         }
         if (ok)
             ok = mbarrier_wait(acc_done, 0, abort_flag, p.counters, 316);
         if (ok) {
             tcgen05_fence_after();
-#pragma unroll
-            for (int which = 0; which < 2; ++which) { // dK then dV
-                uint32_t a[32];
-                tmem_load_32x32_async((which == 0 ? tmem_dk : tmem_dv) + lane_base, a);
-                tmem_wait_load(a);
-                if (key < p.context) {
-                    bf16 *out = p.dqkv + (int64_t(row0) + key) * 3 * p.width + (which + 1) * p.width + h * HeadSize +
-                                half * 32;
-#pragma unroll
-                    for (int g = 0; g < 4; ++g) {
-                        float v[8];
-#pragma unroll
-                        for (int e = 0; e < 8; ++e)
-                            v[e] = __uint_as_float(a[g * 8 + e]);
-                        store8(out + g * 8, v);
-                    }
-                }
-            }
+            bf16 *out = p.dqkv + (int64_t(row0) + key) * 3 * p.width + h * HeadSize + half * 32;
+            const uint32_t lanes = (uint32_t(quarter * 32) << 16) + half * 32;
+            store_accumulator(tmem_dk + lanes, out + p.width, p.scale, key < p.context);
+            store_accumulator(tmem_dv + lanes, out + 2 * p.width, 1.f, key < p.context);
         }
     }
     __syncthreads();
@@ -704,11 +772,11 @@ void launch_flash_attention_backward(const void *qkv, const void *dout, const fl
     p.counters = counters;
     const uint64_t rows = uint64_t(batch) * context;
     CUtensorMap qkv128 = make_map_bf16(qkv, uint64_t(3) * width, rows, 1, uint64_t(3) * width, 0, HeadSize, 128);
-    CUtensorMap qkv64 = make_map_bf16(qkv, uint64_t(3) * width, rows, 1, uint64_t(3) * width, 0, HeadSize, 64);
+    CUtensorMap qkv32 = make_map_bf16(qkv, uint64_t(3) * width, rows, 1, uint64_t(3) * width, 0, HeadSize, Step);
     CUtensorMap do128 = make_map_bf16(dout, width, rows, 1, width, 0, HeadSize, 128);
-    CUtensorMap do64 = make_map_bf16(dout, width, rows, 1, width, 0, HeadSize, 64);
+    CUtensorMap do32 = make_map_bf16(dout, width, rows, 1, width, 0, HeadSize, Step);
     const int grid = batch * heads * p.tiles;
-    flash_dkv_kernel<<<grid, BackwardThreads, DkvShared, s>>>(qkv128, qkv64, do64, p);
-    flash_dq_kernel<<<grid, BackwardThreads, DqShared, s>>>(qkv128, qkv64, do128, p);
+    flash_dkv_kernel<<<grid, BackwardThreads, DkvShared, s>>>(qkv128, qkv32, do32, p);
+    flash_dq_kernel<<<grid, BackwardThreads, DqShared, s>>>(qkv128, qkv32, do128, p);
     CHECK_CUDA(cudaGetLastError());
 }

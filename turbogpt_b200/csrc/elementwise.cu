@@ -237,27 +237,28 @@ template <class T> __global__ void __launch_bounds__(256) norm_kernel(NormArgs a
 // columns and lane), so x is read once; scale and bias are read once per thread.
 template <int V> __device__ __forceinline__ void row_moments(int kind, const float (&x)[V][8], int width,
                                                             float &mean, float &inv) {
-    float sum = 0, squares = 0;
+    // four interleaved partial sums per quantity: the additions of a row are not one long chain
+    float sums[4] = {0, 0, 0, 0}, squares[4] = {0, 0, 0, 0};
 #pragma unroll
     for (int v = 0; v < V; ++v)
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-            sum += x[v][j];
-            squares += x[v][j] * x[v][j];
+            sums[j % 4] += x[v][j];
+            squares[j % 4] += x[v][j] * x[v][j];
         }
     if (kind == TG_NORM_RMS) {
         mean = 0;
-        inv = rsqrtf(warp_sum(squares) / width + 1e-6f);
+        inv = rsqrtf(warp_sum((squares[0] + squares[1]) + (squares[2] + squares[3])) / width + 1e-6f);
         return;
     }
-    mean = warp_sum(sum) / width;
-    float centred = 0;
+    mean = warp_sum((sums[0] + sums[1]) + (sums[2] + sums[3])) / width;
+    float centred[4] = {0, 0, 0, 0};
 #pragma unroll
     for (int v = 0; v < V; ++v)
 #pragma unroll
         for (int j = 0; j < 8; ++j)
-            centred += (x[v][j] - mean) * (x[v][j] - mean);
-    inv = rsqrtf(warp_sum(centred) / width + 1e-5f);
+            centred[j % 4] += (x[v][j] - mean) * (x[v][j] - mean);
+    inv = rsqrtf(warp_sum((centred[0] + centred[1]) + (centred[2] + centred[3])) / width + 1e-5f);
 }
 template <class T, int V> __global__ void __launch_bounds__(256, 4) norm_rows_kernel(NormArgs a) {
     __shared__ __align__(16) float sw[V * 256], sb[V * 256]; // FP32 scale and bias, shared by the block's rows
@@ -362,23 +363,23 @@ template <class T> __global__ void __launch_bounds__(256) norm_backward_kernel(N
     for (int c = threadIdx.x; c < 2 * a.width; c += blockDim.x)
         a.partial[int64_t(blockIdx.x) * 2 * a.width + c] = sums[c];
 }
-// 32 columns per block, 8 threads per column: thread g sums blocks g, g+8, ...; the eight
-// sums are added in order.  Same result on every run.
+// 8 columns per block, 32 threads per column: thread g sums blocks g, g+32, ...; the 32 sums are
+// added in order.  Same result on every run.
 __global__ void __launch_bounds__(256) norm_backward_reduce_kernel(const float *partial, float *dscale,
                                                                    float *dbias, int width, int blocks) {
-    __shared__ float sums[8][33];
-    const int lane = threadIdx.x % 32, group = threadIdx.x / 32;
-    const int c = blockIdx.x * 32 + lane;
+    __shared__ float sums[32][9];
+    const int column = threadIdx.x % 8, group = threadIdx.x / 8;
+    const int c = blockIdx.x * 8 + column;
     float sum = 0;
     if (c < 2 * width)
-        for (int b = group; b < blocks; b += 8)
+        for (int b = group; b < blocks; b += 32)
             sum += partial[int64_t(b) * 2 * width + c];
-    sums[group][lane] = sum;
+    sums[group][column] = sum;
     __syncthreads();
     if (group == 0 && c < 2 * width) {
         float total = 0;
-        for (int g = 0; g < 8; ++g)
-            total += sums[g][lane];
+        for (int g = 0; g < 32; ++g)
+            total += sums[g][column];
         if (c < width)
             dscale[c] = total;
         else if (dbias)
@@ -410,7 +411,7 @@ template <class T, int V> __global__ void __launch_bounds__(256, 2) norm_backwar
         }
         float mean, inv;
         row_moments<V>(a.kind, x, a.width, mean, inv);
-        float sum_dz = 0, sum_dzz = 0;
+        float part_dz[4] = {0, 0, 0, 0}, part_dzz[4] = {0, 0, 0, 0};
 #pragma unroll
         for (int v = 0; v < V; ++v) {
             float w[8];
@@ -419,15 +420,16 @@ template <class T, int V> __global__ void __launch_bounds__(256, 2) norm_backwar
             for (int j = 0; j < 8; ++j) {
                 const float z = (x[v][j] - mean) * inv, dz = g[v][j] * w[j];
                 x[v][j] = z; // keep the normalised value
-                sum_dz += dz;
-                sum_dzz += dz * z;
+                part_dz[j % 4] += dz;
+                part_dzz[j % 4] += dz * z;
                 dw[v][j] += g[v][j] * z;
                 db[v][j] += g[v][j];
                 g[v][j] = dz; // keep dy * scale
             }
         }
-        sum_dzz = warp_sum(sum_dzz) / a.width;
-        sum_dz = a.kind == TG_NORM_LAYER ? warp_sum(sum_dz) / a.width : 0.f;
+        const float sum_dzz = warp_sum((part_dzz[0] + part_dzz[1]) + (part_dzz[2] + part_dzz[3])) / a.width;
+        const float sum_dz =
+            a.kind == TG_NORM_LAYER ? warp_sum((part_dz[0] + part_dz[1]) + (part_dz[2] + part_dz[3])) / a.width : 0.f;
 #pragma unroll
         for (int v = 0; v < V; ++v) {
             float out[8];
@@ -473,6 +475,7 @@ int norm_backward_blocks(int rows, int sms) {
 }
 void launch_norm_backward(Dtype t, const NormBackwardArgs &a, cudaStream_t s) {
     size_t shared = size_t(2) * a.width * sizeof(float);
+    const int reduce_blocks = blocks_for(2 * a.width, 8);
     if (a.width % 256 == 0 && a.width <= 1024) {
         DISPATCH(t, {
             switch (a.width / 256) {
@@ -482,8 +485,7 @@ void launch_norm_backward(Dtype t, const NormBackwardArgs &a, cudaStream_t s) {
             default: launch_norm_backward_rows<T, 4>(a, s); break;
             }
         });
-        norm_backward_reduce_kernel<<<blocks_for(2 * a.width, 32), 256, 0, s>>>(a.partial, a.dscale, a.dbias,
-                                                                              a.width, a.blocks);
+        norm_backward_reduce_kernel<<<reduce_blocks, 256, 0, s>>>(a.partial, a.dscale, a.dbias, a.width, a.blocks);
         return;
     }
     DISPATCH(t, {
@@ -492,8 +494,7 @@ void launch_norm_backward(Dtype t, const NormBackwardArgs &a, cudaStream_t s) {
                                             int(shared)));
         norm_backward_kernel<T><<<a.blocks, 256, shared, s>>>(a);
     });
-    norm_backward_reduce_kernel<<<blocks_for(2 * a.width, 32), 256, 0, s>>>(a.partial, a.dscale, a.dbias, a.width,
-                                                                          a.blocks);
+    norm_backward_reduce_kernel<<<reduce_blocks, 256, 0, s>>>(a.partial, a.dscale, a.dbias, a.width, a.blocks);
 }
 
 // ------------------------------------------------------------------------------------------
