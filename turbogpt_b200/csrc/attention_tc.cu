@@ -382,24 +382,27 @@ flash_dq_kernel(const __grid_constant__ CUtensorMap map_qkv128, const __grid_con
         if (elect_one()) {
             const uint32_t idesc_s = instruction_descriptor(BlockM, Step, 0, 0);
             const uint32_t idesc_dq = instruction_descriptor(BlockM, HeadSize, 0, 1);
+            // descriptors are built once; every MMA below only offsets them
+            const uint64_t q_desc = smem_descriptor(smem_q, 16, 1024), do_desc = smem_descriptor(smem_do, 16, 1024),
+                           kv_desc = smem_descriptor(smem_kv, 16, 1024), k_mn_desc = smem_descriptor(smem_kv, 8192, 1024);
             bool ok = mbarrier_wait(qdo_full, 0, abort_flag, p.counters, 302);
             int issued = 0, stage_in = 0; // score products issued so far, and the stage the next one fills
             auto issue_scores = [&]() {
                 const int ring = issued % Ring;
-                const uint32_t k_tile = smem_kv + ring * 2 * StepBytes, v_tile = k_tile + StepBytes;
                 ok = mbarrier_wait(kv_full0 + 8 * ring, (issued / Ring) & 1, abort_flag, p.counters, 303);
                 if (!ok)
                     return;
                 tcgen05_fence_after();
                 const uint32_t t = tmem_base + 64 * stage_in;
+                const uint64_t k_desc = descriptor_at(kv_desc, ring * 2 * StepBytes),
+                               v_desc = descriptor_at(k_desc, StepBytes);
 #pragma unroll
                 for (int ks = 0; ks < HeadSize / 16; ++ks)
-                    tcgen05_mma_bf16(t, smem_descriptor(smem_q + ks * 32, 16, 1024),
-                                     smem_descriptor(k_tile + ks * 32, 16, 1024), idesc_s, ks > 0);
+                    tcgen05_mma_bf16(t, descriptor_at(q_desc, ks * 32), descriptor_at(k_desc, ks * 32), idesc_s, ks > 0);
 #pragma unroll
                 for (int ks = 0; ks < HeadSize / 16; ++ks)
-                    tcgen05_mma_bf16(t + 32, smem_descriptor(smem_do + ks * 32, 16, 1024),
-                                     smem_descriptor(v_tile + ks * 32, 16, 1024), idesc_s, ks > 0);
+                    tcgen05_mma_bf16(t + 32, descriptor_at(do_desc, ks * 32), descriptor_at(v_desc, ks * 32), idesc_s,
+                                     ks > 0);
                 tcgen05_commit(s_full0 + 8 * stage_in);
                 ++issued;
                 stage_in = stage_in + 1 == DqStages ? 0 : stage_in + 1;
@@ -415,12 +418,11 @@ flash_dq_kernel(const __grid_constant__ CUtensorMap map_qkv128, const __grid_con
                     break;
                 tcgen05_fence_after();
                 const int ring = j % Ring;
-                const uint32_t k_tile = smem_kv + ring * 2 * StepBytes;
+                const uint64_t k_desc = descriptor_at(k_mn_desc, ring * 2 * StepBytes);
 #pragma unroll
                 for (int ks = 0; ks < Step / 16; ++ks) // dQ += dS K_j: 16 keys (8 packed columns at 16 ks) at a time
-                    tcgen05_mma_bf16_ts(tmem_dq, tmem_base + 64 * stage + ks * 16,
-                                        smem_descriptor(k_tile + ks * 2048, 8192, 1024), idesc_dq,
-                                        (j > 0 || ks > 0) ? 1u : 0u);
+                    tcgen05_mma_bf16_ts(tmem_dq, tmem_base + 64 * stage + ks * 16, descriptor_at(k_desc, ks * 2048),
+                                        idesc_dq, (j > 0 || ks > 0) ? 1u : 0u);
                 tcgen05_commit(kv_empty0 + 8 * ring);
                 if (issued < blocks)
                     issue_scores(); // reuses the stage whose dS the MMAs issued one step ago have read
@@ -589,24 +591,28 @@ flash_dkv_kernel(const __grid_constant__ CUtensorMap map_qkv128, const __grid_co
         if (elect_one()) {
             const uint32_t idesc_s = instruction_descriptor(BlockN, Step, 0, 0);
             const uint32_t idesc_acc = instruction_descriptor(BlockN, HeadSize, 0, 1);
+            // descriptors are built once; every MMA below only offsets them
+            const uint64_t k_desc = smem_descriptor(smem_k, 16, 1024), v_desc = smem_descriptor(smem_v, 16, 1024),
+                           qdo_desc = smem_descriptor(smem_qdo, 16, 1024),
+                           qdo_mn_desc = smem_descriptor(smem_qdo, 8192, 1024);
             bool ok = mbarrier_wait(kv_full, 0, abort_flag, p.counters, 312);
             int issued = 0;
             auto issue_scores = [&]() {
                 const int ring = issued % Ring;
-                const uint32_t q_tile = smem_qdo + ring * 2 * StepBytes, do_tile = q_tile + StepBytes;
                 ok = mbarrier_wait(qdo_full0 + 8 * ring, (issued / Ring) & 1, abort_flag, p.counters, 313);
                 if (!ok)
                     return;
                 tcgen05_fence_after();
                 const uint32_t t = tmem_base + 64 * (issued % DkvStages);
+                const uint64_t q_desc = descriptor_at(qdo_desc, ring * 2 * StepBytes),
+                               do_desc = descriptor_at(q_desc, StepBytes);
 #pragma unroll
                 for (int ks = 0; ks < HeadSize / 16; ++ks) // S^T = K Q_i^T
-                    tcgen05_mma_bf16(t, smem_descriptor(smem_k + ks * 32, 16, 1024),
-                                     smem_descriptor(q_tile + ks * 32, 16, 1024), idesc_s, ks > 0);
+                    tcgen05_mma_bf16(t, descriptor_at(k_desc, ks * 32), descriptor_at(q_desc, ks * 32), idesc_s, ks > 0);
 #pragma unroll
                 for (int ks = 0; ks < HeadSize / 16; ++ks) // dP^T = V dO_i^T
-                    tcgen05_mma_bf16(t + 32, smem_descriptor(smem_v + ks * 32, 16, 1024),
-                                     smem_descriptor(do_tile + ks * 32, 16, 1024), idesc_s, ks > 0);
+                    tcgen05_mma_bf16(t + 32, descriptor_at(v_desc, ks * 32), descriptor_at(do_desc, ks * 32), idesc_s,
+                                     ks > 0);
                 tcgen05_commit(s_full0 + 8 * (issued % DkvStages));
                 ++issued;
             };
@@ -620,16 +626,17 @@ flash_dkv_kernel(const __grid_constant__ CUtensorMap map_qkv128, const __grid_co
                 if (!ok)
                     break;
                 tcgen05_fence_after();
-                const uint32_t q_tile = smem_qdo + ring * 2 * StepBytes, do_tile = q_tile + StepBytes;
+                const uint64_t q_desc = descriptor_at(qdo_mn_desc, ring * 2 * StepBytes),
+                               do_desc = descriptor_at(q_desc, StepBytes);
                 const uint32_t t = tmem_base + 64 * stage;
 #pragma unroll
                 for (int ks = 0; ks < Step / 16; ++ks) // dV += P^T dO_i
-                    tcgen05_mma_bf16_ts(tmem_dv, t + ks * 16, smem_descriptor(do_tile + ks * 2048, 8192, 1024),
-                                        idesc_acc, (i > 0 || ks > 0) ? 1u : 0u);
+                    tcgen05_mma_bf16_ts(tmem_dv, t + ks * 16, descriptor_at(do_desc, ks * 2048), idesc_acc,
+                                        (i > 0 || ks > 0) ? 1u : 0u);
 #pragma unroll
                 for (int ks = 0; ks < Step / 16; ++ks) // dK += dS^T Q_i
-                    tcgen05_mma_bf16_ts(tmem_dk, t + 32 + ks * 16, smem_descriptor(q_tile + ks * 2048, 8192, 1024),
-                                        idesc_acc, (i > 0 || ks > 0) ? 1u : 0u);
+                    tcgen05_mma_bf16_ts(tmem_dk, t + 32 + ks * 16, descriptor_at(q_desc, ks * 2048), idesc_acc,
+                                        (i > 0 || ks > 0) ? 1u : 0u);
                 tcgen05_commit(qdo_empty0 + 8 * ring);
                 if (issued < blocks)
                     issue_scores(); // into the stage the products above have just read

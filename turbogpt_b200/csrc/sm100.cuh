@@ -356,6 +356,17 @@ __device__ __forceinline__ uint64_t smem_descriptor(uint32_t address, uint32_t l
     d |= uint64_t(2) << 61; // 128-byte swizzle
     return d;
 }
+// The same descriptor `bytes` further into shared memory (the address field holds address / 16 in
+// the low 14 bits; tiles never wrap it).  One 32-bit add instead of rebuilding the descriptor:
+// the MMA-issuing thread is a serial bottleneck when the MMAs are small.
+__device__ __forceinline__ uint64_t descriptor_at(uint64_t descriptor, uint32_t bytes) {
+    uint32_t lo, hi;
+    asm("mov.b64 {%0, %1}, %2;" : "=r"(lo), "=r"(hi) : "l"(descriptor));
+    lo += bytes >> 4;
+    uint64_t moved;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(moved) : "r"(lo), "r"(hi));
+    return moved;
+}
 // Instruction descriptor: BF16 x BF16 -> FP32, M x N tile, operand majorness (0 = K, 1 = MN).
 __host__ __device__ inline uint32_t instruction_descriptor(int m, int n, int a_mn_major, int b_mn_major) {
     return (1u << 4) | (1u << 7) | (1u << 10) | (uint32_t(a_mn_major) << 15) | (uint32_t(b_mn_major) << 16) |
