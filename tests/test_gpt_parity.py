@@ -145,3 +145,59 @@ def test_muon_on_the_tensor_core_path():
         assert relative(actual[mask] - w[mask], opt.w[mask] - w[mask]) < 1e-4
         np.testing.assert_allclose(actual[mask], opt.w[mask], atol=2e-6, rtol=2e-5)
         assert relative(actual - w, opt.w - w) < .04  # verify.py:101's bound for the Muon part
+
+
+def _structured_bytes(size, seed):
+    """Learnable bytes: an order-1 Markov chain with sparse (Dirichlet 0.05) transition rows."""
+    rng = np.random.default_rng(seed)
+    table = rng.gamma(.05, size=(256, 256)) + 1e-30
+    cdf = np.cumsum(table / table.sum(1, keepdims=True), axis=1)
+    out = np.empty(size, np.uint8)
+    u = rng.random(size)
+    state = 0
+    for i in range(size):
+        state = min(int(np.searchsorted(cdf[state], u[i])), 255)
+        out[i] = state
+    return out
+
+
+def test_bf16_loss_curve_tracks_fp32_over_200_steps():
+    """The BF16 engine against the same engine in FP32 check mode, 200 OneCycle steps on the same
+    sampled bytes: the loss curves (means over windows of 10 steps) stay within 1 % of each other
+    and the model learns."""
+    depth, width, heads, context, batch, steps = 4, 256, 4, 256, 8, 200
+    arch, model, w, _, _ = fixture(depth, width, heads, context, batch, False)
+    data = _structured_bytes(1 << 16, 5)
+    curves = []
+    for precision in (bridge.PRECISION_BF16, bridge.PRECISION_FP32):
+        base = Config(depth=depth, context=context, batch=batch, learning_rate=1e-3, clip=1.0)
+        with Native(ConfigEx.gpt(base, width, heads, precision=precision)) as engine:
+            engine.set_weights(w)
+            engine.set_data(data)
+            engine.set_onecycle(steps)
+            engine.train(steps)
+            curves.append(engine.training_losses(steps).mean(1).reshape(-1, 10).mean(1))
+    bf16, fp32 = curves
+    np.testing.assert_allclose(bf16, fp32, rtol=.01)
+    assert fp32[-1] < .8 * fp32[0]
+
+
+def test_graph_replay_is_bit_identical_to_direct_launches():
+    """tg_train replays a CUDA graph of the step after the first one; with TG_FLAG_NO_GRAPH every
+    kernel is launched directly.  Every kernel is deterministic, so weights and losses agree bit
+    for bit, also when training continues in a second call."""
+    depth, width, heads, context, batch = 2, 128, 2, 128, 4
+    arch, model, w, _, _ = fixture(depth, width, heads, context, batch, False)
+    data = np.random.default_rng(7).integers(0, 64, 1 << 14, dtype=np.uint8)
+    results = []
+    for flags in (0, bridge.FLAG_NO_GRAPH):
+        base = Config(depth=depth, context=context, batch=batch, learning_rate=1e-3, clip=1.0)
+        with Native(ConfigEx.gpt(base, width, heads, flags=flags)) as engine:
+            engine.set_weights(w)
+            engine.set_data(data)
+            engine.train(5)
+            first = engine.training_losses(5).copy()
+            engine.train(4)
+            results.append((first, engine.training_losses(4).copy(), engine.weights()))
+    for a, b in zip(*results):
+        np.testing.assert_array_equal(a, b)

@@ -308,12 +308,14 @@ void launch_norm(Dtype t, const NormArgs &a, cudaStream_t s) {
 
 // dx = (dz - [mean(dz)] - z * mean(dz * z)) * inv with dz = dy * w, z the normalised input;
 // rounded to the activation type, then added to the running residual gradient with a second
-// rounding (reference cuda/ops.cuh:67-80).  Scale/bias gradients: shared-memory sums per block,
-// then a fixed-order sum over blocks.
+// rounding (reference cuda/ops.cuh:67-80).  Scale/bias gradients: each warp sums its rows in its own
+// slice of shared memory (a lane owns its columns there, so no atomics), the warps are added in
+// order, then a fixed-order sum over blocks: the same bits on every run.
 template <class T> __global__ void __launch_bounds__(256) norm_backward_kernel(NormBackwardArgs a) {
-    extern __shared__ float sums[]; // [2][width]
+    extern __shared__ float sums[]; // [warps][2][width]
     const int lane = threadIdx.x % 32, warps = blockDim.x / 32;
-    for (int c = threadIdx.x; c < 2 * a.width; c += blockDim.x)
+    float *mine = sums + (threadIdx.x / 32) * 2 * a.width;
+    for (int c = threadIdx.x; c < warps * 2 * a.width; c += blockDim.x)
         sums[c] = 0;
     __syncthreads();
     for (int row = blockIdx.x * warps + threadIdx.x / 32; row < a.rows; row += gridDim.x * warps) {
@@ -332,9 +334,9 @@ template <class T> __global__ void __launch_bounds__(256) norm_backward_kernel(N
                 float z = (v[j] - mean) * inv, dz = g[j] * w[j];
                 sum_dz += dz;
                 sum_dzz += dz * z;
-                atomicAdd(&sums[c + j], g[j] * z);
+                mine[c + j] += g[j] * z;
                 if (a.kind == TG_NORM_LAYER)
-                    atomicAdd(&sums[a.width + c + j], g[j]);
+                    mine[a.width + c + j] += g[j];
             }
         }
         sum_dzz = warp_sum(sum_dzz) / a.width;
@@ -360,8 +362,12 @@ template <class T> __global__ void __launch_bounds__(256) norm_backward_kernel(N
         }
     }
     __syncthreads();
-    for (int c = threadIdx.x; c < 2 * a.width; c += blockDim.x)
-        a.partial[int64_t(blockIdx.x) * 2 * a.width + c] = sums[c];
+    for (int c = threadIdx.x; c < 2 * a.width; c += blockDim.x) {
+        float total = 0;
+        for (int w = 0; w < warps; ++w)
+            total += sums[w * 2 * a.width + c];
+        a.partial[int64_t(blockIdx.x) * 2 * a.width + c] = total;
+    }
 }
 // 8 columns per block, 32 threads per column: thread g sums blocks g, g+32, ...; the 32 sums are
 // added in order.  Same result on every run.
@@ -488,11 +494,16 @@ void launch_norm_backward(Dtype t, const NormBackwardArgs &a, cudaStream_t s) {
         norm_backward_reduce_kernel<<<reduce_blocks, 256, 0, s>>>(a.partial, a.dscale, a.dbias, a.width, a.blocks);
         return;
     }
+    // as many warps per block (up to 8) as 200 KB of per-warp sums allow
+    int warps = 8;
+    while (warps > 1 && shared * warps > 200 * 1024)
+        warps /= 2;
+    shared *= warps;
     DISPATCH(t, {
         if (shared > 48 * 1024)
             CHECK_CUDA(cudaFuncSetAttribute(norm_backward_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                             int(shared)));
-        norm_backward_kernel<T><<<a.blocks, 256, shared, s>>>(a);
+        norm_backward_kernel<T><<<a.blocks, warps * 32, shared, s>>>(a);
     });
     norm_backward_reduce_kernel<<<reduce_blocks, 256, 0, s>>>(a.partial, a.dscale, a.dbias, a.width, a.blocks);
 }
