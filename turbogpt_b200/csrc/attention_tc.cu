@@ -2,14 +2,17 @@
 // Replaces the reference's per-(query, head) scalar attention loops (cuda/attention.cuh:33-106)
 // for the scaled architecture: no T x T matrix ever reaches HBM.
 //
-// Forward: one CTA per 128 query rows of one (batch, head).  Warp 0 streams K/V blocks of 128
-// keys with TMA (two stages); warp 1 issues tcgen05.mma: S = Q K^T into tensor memory, then
-// O_blk = P V with P read back from tensor memory as the A operand; warps 2-5 own one query
-// row per thread (the TMEM lane), so the online-softmax row maximum and sum are thread-local:
-// one pass over S (128 registers), exp2 and BF16 packing, P written to TMEM; the output accumulates
-// in tensor memory and is rescaled only when the row maximum has grown by more than 2^8.  Two CTAs
-// share an SM (256 TMEM columns and 83 KB of shared memory each), so one CTA's exponentials overlap
-// the other's MMAs.
+// Forward: one CTA per 128 query rows of one (batch, head).  Warp 0 streams K/V in steps of 64
+// keys with TMA (four-slot ring); warp 1 issues tcgen05.mma: S = Q K^T into tensor memory, then
+// O += P V with P read back from tensor memory as the A operand.  The exponential (16 per clock
+// and SM) bounds the kernel, so the softmax work is arranged to keep that unit busy: the steps
+// alternate between two chains, each a complete online softmax with its own score buffer,
+// reference maximum, row sum and output accumulator in tensor memory and its own four warps (thread
+// = query row = TMEM lane, so maxima and sums are thread-local).  While one chain is in its
+// exponentials the other waits for its scores or hands its probabilities to the MMA thread; the
+// chains never wait for each other and are merged once at the end.  An accumulator is rescaled only
+// when its row maximum has grown by more than 2^8.  Two CTAs share an SM (256 TMEM columns and 84 KB
+// of shared memory each).
 #include "device_utils.cuh"
 #include "sm100.cuh"
 
@@ -18,9 +21,11 @@ using namespace sm100;
 namespace {
 constexpr int BlockM = 128, BlockN = 128, HeadSize = 64;
 constexpr int TileBytes = 128 * HeadSize * 2; // 16 KB: a Q, K or V tile
-constexpr int ForwardThreads = 192;
-constexpr int ForwardShared = TileBytes * 5 + 1024 + 256; // Q + 2 x (K, V) + alignment + barriers
-constexpr int ForwardTmemColumns = 256;                   // S 0..127 | P 128..191 | O_blk 192..255
+constexpr int KeyStep = 64, KeyBytes = KeyStep * HeadSize * 2; // the forward pass takes 64 keys (8 KB of K, of V) per step
+constexpr int ForwardRing = 4;                                 // shared-memory ring of (K, V) steps
+constexpr int ForwardThreads = 320;                            // warp 0 TMA, warp 1 MMA, 8 softmax warps
+constexpr int ForwardShared = TileBytes + ForwardRing * 2 * KeyBytes + 2048 + 1024 + 256; // Q, ring, merge buffer
+constexpr int ForwardTmemColumns = 256; // per chain: 64 score columns, 64 output columns
 
 struct ForwardParams {
     bf16 *out;
@@ -37,14 +42,16 @@ __device__ __forceinline__ float fast_exp2(float x) {
 }
 
 __global__ void __launch_bounds__(ForwardThreads, 2)
-flash_forward_kernel(const __grid_constant__ CUtensorMap map_qkv, ForwardParams p) {
+flash_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv,
+                     ForwardParams p) {
     extern __shared__ uint8_t raw_shared[];
     const uint32_t base = (smem_address(raw_shared) + 1023u) & ~1023u;
     uint8_t *aligned = raw_shared + (base - smem_address(raw_shared));
-    uint64_t *barriers = reinterpret_cast<uint64_t *>(aligned + 5 * TileBytes);
-    const uint32_t q_full = smem_address(barriers), kv_full0 = q_full + 8, kv_empty0 = kv_full0 + 16,
-                   s_full = kv_empty0 + 16, p_full = s_full + 8, o_full = p_full + 8;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(barriers + 8);
+    float *exchange = reinterpret_cast<float *>(aligned + TileBytes + ForwardRing * 2 * KeyBytes); // [2 chains][max | sum][128 rows]
+    uint64_t *barriers = reinterpret_cast<uint64_t *>(exchange + 4 * BlockM);
+    const uint32_t q_full = smem_address(barriers), kv_full0 = q_full + 8, kv_empty0 = kv_full0 + 8 * ForwardRing,
+                   s_full0 = kv_empty0 + 8 * ForwardRing, p_full0 = s_full0 + 16, o_full0 = p_full0 + 16;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(barriers + 1 + 2 * ForwardRing + 6);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
     const uint32_t smem_q = base, smem_kv = base + TileBytes;
 
@@ -53,21 +60,25 @@ flash_forward_kernel(const __grid_constant__ CUtensorMap map_qkv, ForwardParams 
     const int pairs = p.batch * p.heads;
     const int tile = p.tiles - 1 - int(blockIdx.x / pairs);
     const int bh = blockIdx.x % pairs, b = bh / p.heads, h = bh % p.heads;
-    const int blocks = tile + 1; // causal: key blocks 0..tile
     const int row0 = b * p.context; // first row of this sequence in the packed qkv matrix
+    const int last_key = min(p.context, (tile + 1) * BlockM);
+    const int steps = (last_key + KeyStep - 1) / KeyStep; // causal: keys 0 .. last_key - 1, 64 per step
 
     if (threadIdx.x == 0) {
         mbarrier_init(q_full, 1);
-        for (int s = 0; s < 2; ++s) {
+        for (int s = 0; s < ForwardRing; ++s) {
             mbarrier_init(kv_full0 + 8 * s, 1);
             mbarrier_init(kv_empty0 + 8 * s, 1);
         }
-        mbarrier_init(s_full, 1);
-        mbarrier_init(p_full, 4);
-        mbarrier_init(o_full, 1);
+        for (int c = 0; c < 2; ++c) {
+            mbarrier_init(s_full0 + 8 * c, 1);
+            mbarrier_init(p_full0 + 8 * c, 4);
+            mbarrier_init(o_full0 + 8 * c, 1);
+        }
         *abort_flag = 0;
         fence_barrier_init();
-        prefetch_map(&map_qkv);
+        prefetch_map(&map_q);
+        prefetch_map(&map_kv);
     }
     if (warp == 1) {
         tmem_alloc(smem_address(tmem_slot), ForwardTmemColumns);
@@ -77,185 +88,211 @@ flash_forward_kernel(const __grid_constant__ CUtensorMap map_qkv, ForwardParams 
     __syncthreads();
     tcgen05_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    const uint32_t tmem_s = tmem_base, tmem_p = tmem_base + 128, tmem_o = tmem_base + 192;
+    // chain c: scores of its steps at 64 c (the probabilities pack into the first 32 of those columns),
+    // its output accumulator at 128 + 64 c
+    const uint32_t tmem_s0 = tmem_base, tmem_o0 = tmem_base + 128;
 
     if (warp == 0) {
         if (elect_one()) {
             mbarrier_expect_tx(q_full, TileBytes);
-            tma_load_3d(smem_q, &map_qkv, h * HeadSize, row0 + tile * BlockM, 0, q_full);
-            for (int j = 0; j < blocks; ++j) {
-                const int stage = j & 1;
-                if (!mbarrier_wait(kv_empty0 + 8 * stage, ((j >> 1) & 1) ^ 1, abort_flag, p.counters, 201))
+            tma_load_3d(smem_q, &map_q, h * HeadSize, row0 + tile * BlockM, 0, q_full);
+            for (int j = 0; j < steps; ++j) {
+                const int ring = j % ForwardRing;
+                if (!mbarrier_wait(kv_empty0 + 8 * ring, ((j / ForwardRing) & 1) ^ 1, abort_flag, p.counters, 201))
                     break;
-                const uint32_t bar = kv_full0 + 8 * stage, dst = smem_kv + stage * 2 * TileBytes;
-                mbarrier_expect_tx(bar, 2 * TileBytes);
-                tma_load_3d(dst, &map_qkv, p.width + h * HeadSize, row0 + j * BlockN, 0, bar);
-                tma_load_3d(dst + TileBytes, &map_qkv, 2 * p.width + h * HeadSize, row0 + j * BlockN, 0, bar);
+                const uint32_t bar = kv_full0 + 8 * ring, dst = smem_kv + ring * 2 * KeyBytes;
+                mbarrier_expect_tx(bar, 2 * KeyBytes);
+                tma_load_3d(dst, &map_kv, p.width + h * HeadSize, row0 + j * KeyStep, 0, bar);
+                tma_load_3d(dst + KeyBytes, &map_kv, 2 * p.width + h * HeadSize, row0 + j * KeyStep, 0, bar);
             }
         }
     } else if (warp == 1) {
         if (elect_one()) {
-            const uint32_t idesc_s = instruction_descriptor(BlockM, BlockN, 0, 0);
+            const uint32_t idesc_s = instruction_descriptor(BlockM, KeyStep, 0, 0);
             const uint32_t idesc_o = instruction_descriptor(BlockM, HeadSize, 0, 1);
-            auto issue_s = [&](int j) { // S = Q K_j^T: four 16-deep steps along the head dimension
-                const uint32_t k_tile = smem_kv + (j & 1) * 2 * TileBytes;
+            const uint64_t q_desc = smem_descriptor(smem_q, 16, 1024), k_desc0 = smem_descriptor(smem_kv, 16, 1024),
+                           v_desc0 = smem_descriptor(smem_kv + KeyBytes, 8192, 1024);
+            bool ok = mbarrier_wait(q_full, 0, abort_flag, p.counters, 202);
+            int issued = 0;
+            auto issue_scores = [&]() { // S = Q K_j^T into the buffer of chain j % 2
+                const int ring = issued % ForwardRing, chain = issued & 1;
+                ok = mbarrier_wait(kv_full0 + 8 * ring, (issued / ForwardRing) & 1, abort_flag, p.counters, 203);
+                if (!ok)
+                    return;
+                tcgen05_fence_after();
+                const uint64_t k_desc = descriptor_at(k_desc0, ring * 2 * KeyBytes);
 #pragma unroll
                 for (int ks = 0; ks < HeadSize / 16; ++ks)
-                    tcgen05_mma_bf16(tmem_s, smem_descriptor(smem_q + ks * 32, 16, 1024),
-                                     smem_descriptor(k_tile + ks * 32, 16, 1024), idesc_s, ks > 0);
-                tcgen05_commit(s_full);
+                    tcgen05_mma_bf16(tmem_s0 + 64 * chain, descriptor_at(q_desc, ks * 32), descriptor_at(k_desc, ks * 32),
+                                     idesc_s, ks > 0);
+                tcgen05_commit(s_full0 + 8 * chain);
+                ++issued;
             };
-            bool ok = mbarrier_wait(q_full, 0, abort_flag, p.counters, 202) &&
-                      mbarrier_wait(kv_full0, 0, abort_flag, p.counters, 203);
-            if (ok) {
-                tcgen05_fence_after();
-                issue_s(0);
-            }
-            for (int j = 0; j < blocks && ok; ++j) {
-                ok = mbarrier_wait(p_full, j & 1, abort_flag, p.counters, 204);
+            if (ok)
+                issue_scores();
+            if (ok && steps > 1)
+                issue_scores();
+            for (int j = 0; j < steps && ok; ++j) {
+                const int chain = j & 1, ring = j % ForwardRing;
+                ok = mbarrier_wait(p_full0 + 8 * chain, (j >> 1) & 1, abort_flag, p.counters, 204);
                 if (!ok)
                     break;
                 tcgen05_fence_after();
-                const uint32_t v_tile = smem_kv + (j & 1) * 2 * TileBytes + TileBytes;
+                const uint64_t v_desc = descriptor_at(v_desc0, ring * 2 * KeyBytes);
 #pragma unroll
-                for (int ks = 0; ks < BlockN / 16; ++ks) // O += P V_j: eight 16-key steps
-                    tcgen05_mma_bf16_ts(tmem_o, tmem_p + ks * 8, smem_descriptor(v_tile + ks * 2048, 8192, 1024),
-                                        idesc_o, (j > 0 || ks > 0) ? 1u : 0u);
-                tcgen05_commit(o_full);
-                tcgen05_commit(kv_empty0 + 8 * (j & 1)); // K_j and V_j are no longer read
-                if (j + 1 < blocks) {
-                    ok = mbarrier_wait(kv_full0 + 8 * ((j + 1) & 1), ((j + 1) >> 1) & 1, abort_flag, p.counters, 205);
-                    if (!ok)
-                        break;
-                    tcgen05_fence_after();
-                    issue_s(j + 1);
-                }
+                for (int ks = 0; ks < KeyStep / 16; ++ks) // O_chain += P V_j: four 16-key steps
+                    tcgen05_mma_bf16_ts(tmem_o0 + 64 * chain, tmem_s0 + 64 * chain + ks * 8,
+                                        descriptor_at(v_desc, ks * 2048), idesc_o, (j > 1 || ks > 0) ? 1u : 0u);
+                tcgen05_commit(o_full0 + 8 * chain);
+                tcgen05_commit(kv_empty0 + 8 * ring); // K_j and V_j are no longer read
+                if (issued < steps)
+                    issue_scores(); // step j + 2 reuses this chain's buffer: issued after the products that read it
             }
         }
     } else {
-        const int quarter = warp % 4;
+        // Eight softmax warps: two per TMEM lane quarter, one for each chain.  A chain takes every
+        // other 64-key step and is a complete online softmax of its own (reference maximum, sum and
+        // output accumulator), so the two never wait for each other; they are merged at the end.
+        const int quarter = warp % 4, chain = (warp - 2) / 4;
         const int row = quarter * 32 + lane;              // query row inside the tile = TMEM lane
         const int position = tile * BlockM + row;          // position inside the sequence
-        const uint32_t lane_base = uint32_t(quarter * 32) << 16;
-        // The output accumulates in tensor memory across key blocks.  Probabilities are taken
-        // relative to a reference maximum that is only moved (and the output rescaled) when the true
-        // maximum has grown by more than 2^8: values stay inside BF16/FP32 range and the final
-        // division by the row sum, accumulated with the same reference, makes the result exact.
+        const int warp_first = tile * BlockM + quarter * 32;
+        const uint32_t lanes = uint32_t(quarter * 32) << 16;
+        const uint32_t tmem_s = tmem_s0 + 64 * chain + lanes, tmem_o = tmem_o0 + 64 * chain + lanes;
+        // Probabilities are taken relative to a reference maximum that is only moved (and the output
+        // rescaled) when the true maximum has grown by more than 2^8: values stay inside BF16/FP32 range
+        // and the final division by the row sum, accumulated with the same reference, makes the result exact.
         float reference_max = -CUDART_INF_F, running_sum = 0.f;
         bool ok = true;
-        for (int j = 0; j < blocks; ++j) {
-            ok = mbarrier_wait(s_full, j & 1, abort_flag, p.counters, 206);
+        int mine = 0; // steps this chain has taken
+        for (int j = chain; j < steps; j += 2, ++mine) {
+            ok = mbarrier_wait(s_full0 + 8 * chain, mine & 1, abort_flag, p.counters, 206);
             if (!ok)
                 break;
             tcgen05_fence_after();
-            uint32_t s0[32], s1[32], s2[32], s3[32];
-            tmem_load_32x32_async(tmem_s + lane_base, s0);
-            tmem_load_32x32_async(tmem_s + lane_base + 32, s1);
-            tmem_load_32x32_async(tmem_s + lane_base + 64, s2);
-            tmem_load_32x32_async(tmem_s + lane_base + 96, s3);
-            tmem_wait_load(s0);
-            tmem_wait_load(s1);
-            tmem_wait_load(s2);
-            tmem_wait_load(s3);
-            if (j == tile) { // diagonal block: keys after the query do not exist
-#pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    if (i > row) s0[i] = 0xff800000u;
-                    if (32 + i > row) s1[i] = 0xff800000u;
-                    if (64 + i > row) s2[i] = 0xff800000u;
-                    if (96 + i > row) s3[i] = 0xff800000u;
-                }
-            }
+            const int key0 = j * KeyStep;
+            const bool diagonal = key0 + KeyStep - 1 > warp_first; // some key of the step lies after some query of the warp
             float block_max = -CUDART_INF_F;
+            { // first pass over the scores: the row maximum
+                uint32_t s0[32], s1[32];
+                tmem_load_32x32_async(tmem_s, s0);
+                tmem_load_32x32_async(tmem_s + 32, s1);
+                tmem_wait_load(s0);
+                tmem_wait_load(s1);
+                if (diagonal) {
 #pragma unroll
-            for (int i = 0; i < 32; ++i)
-                block_max = fmaxf(fmaxf(block_max, fmaxf(__uint_as_float(s0[i]), __uint_as_float(s1[i]))),
-                                  fmaxf(__uint_as_float(s2[i]), __uint_as_float(s3[i])));
-            // All earlier P V products must have completed before P is overwritten or O rescaled.
-            if (j > 0) {
-                ok = mbarrier_wait(o_full, (j - 1) & 1, abort_flag, p.counters, 207);
+                    for (int i = 0; i < 32; ++i) {
+                        if (key0 + i > position) s0[i] = 0xff800000u;
+                        if (key0 + 32 + i > position) s1[i] = 0xff800000u;
+                    }
+                }
+                float m0 = -CUDART_INF_F, m1 = -CUDART_INF_F;
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                    m0 = fmaxf(m0, fmaxf(__uint_as_float(s0[i]), __uint_as_float(s1[i])));
+                    m1 = fmaxf(m1, fmaxf(__uint_as_float(s0[i + 1]), __uint_as_float(s1[i + 1])));
+                }
+                block_max = fmaxf(m0, m1);
+            }
+            const bool grow = (block_max - reference_max) * p.scale_log2 > 8.f; // true for the first unmasked step
+            if (__any_sync(0xffffffffu, grow && reference_max != -CUDART_INF_F)) {
+                // the accumulator is rescaled only between this chain's products: wait for the last one
+                ok = mbarrier_wait(o_full0 + 8 * chain, (mine - 1) & 1, abort_flag, p.counters, 207);
                 if (!ok)
                     break;
                 tcgen05_fence_after();
-            }
-            const bool grow = (block_max - reference_max) * p.scale_log2 > 8.f; // also true for j == 0
-            if (__any_sync(0xffffffffu, grow) && j > 0) {
-                const float new_max = grow ? block_max : reference_max;
-                const float correction = fast_exp2((reference_max - new_max) * p.scale_log2);
+                const float correction =
+                    grow && reference_max != -CUDART_INF_F ? fast_exp2((reference_max - block_max) * p.scale_log2) : 1.f;
                 running_sum *= correction;
 #pragma unroll 1
                 for (int half = 0; half < 2; ++half) { // 32 columns at a time keeps the register count down
                     uint32_t a[32];
-                    tmem_load_32x32_async(tmem_o + lane_base + half * 32, a);
+                    tmem_load_32x32_async(tmem_o + half * 32, a);
                     tmem_wait_load(a);
 #pragma unroll
                     for (int i = 0; i < 32; ++i)
                         a[i] = __float_as_uint(__uint_as_float(a[i]) * correction);
-                    tmem_store_32x32(tmem_o + lane_base + half * 32, a);
+                    tmem_store_32x32(tmem_o + half * 32, a);
                 }
             }
             if (grow)
                 reference_max = block_max;
-            const float offset = reference_max * p.scale_log2;
-            float block_sum = 0.f;
-            {
-                uint32_t packed[32];
+            // a row with nothing unmasked so far (it lies before every key this chain has seen) has
+            // reference_max = -inf: every probability below is exp2(-inf) = 0 with offset 0
+            const float offset = reference_max == -CUDART_INF_F ? 0.f : reference_max * p.scale_log2;
+            float sums[2] = {0.f, 0.f};
+#pragma unroll
+            for (int half = 0; half < 2; ++half) { // second pass: exponentials, 32 keys at a time
+                uint32_t s[32], packed[16];
+                tmem_load_32x32_async(tmem_s + half * 32, s);
+                tmem_wait_load(s);
 #pragma unroll
                 for (int i = 0; i < 32; i += 2) {
-                    float p0 = fast_exp2(fmaf(__uint_as_float(s0[i]), p.scale_log2, -offset));
-                    float p1 = fast_exp2(fmaf(__uint_as_float(s0[i + 1]), p.scale_log2, -offset));
-                    float p2 = fast_exp2(fmaf(__uint_as_float(s1[i]), p.scale_log2, -offset));
-                    float p3 = fast_exp2(fmaf(__uint_as_float(s1[i + 1]), p.scale_log2, -offset));
-                    block_sum += (p0 + p1) + (p2 + p3);
+                    float p0 = fast_exp2(fmaf(__uint_as_float(s[i]), p.scale_log2, -offset));
+                    float p1 = fast_exp2(fmaf(__uint_as_float(s[i + 1]), p.scale_log2, -offset));
+                    if (diagonal) {
+                        if (key0 + half * 32 + i > position) p0 = 0.f;
+                        if (key0 + half * 32 + i + 1 > position) p1 = 0.f;
+                    }
+                    sums[0] += p0;
+                    sums[1] += p1;
                     packed[i / 2] = pack_bf16(p0, p1);
-                    packed[16 + i / 2] = pack_bf16(p2, p3);
                 }
-                tmem_store_32x32(tmem_p + lane_base, packed);
-            }
-            {
-                uint32_t packed[32];
-#pragma unroll
-                for (int i = 0; i < 32; i += 2) {
-                    float p0 = fast_exp2(fmaf(__uint_as_float(s2[i]), p.scale_log2, -offset));
-                    float p1 = fast_exp2(fmaf(__uint_as_float(s2[i + 1]), p.scale_log2, -offset));
-                    float p2 = fast_exp2(fmaf(__uint_as_float(s3[i]), p.scale_log2, -offset));
-                    float p3 = fast_exp2(fmaf(__uint_as_float(s3[i + 1]), p.scale_log2, -offset));
-                    block_sum += (p0 + p1) + (p2 + p3);
-                    packed[i / 2] = pack_bf16(p0, p1);
-                    packed[16 + i / 2] = pack_bf16(p2, p3);
-                }
-                tmem_store_32x32(tmem_p + lane_base + 32, packed);
+                // the packed half lands on score columns 16 half .. 16 half + 15, which both passes have
+                // finished with (half 1 is read from columns 32 .. 63 before this store is issued)
+                tmem_store_32x16(tmem_s + half * 16, packed);
             }
             tmem_wait_store();
             tcgen05_fence_before();
             __syncwarp();
             if (lane == 0)
-                mbarrier_arrive(p_full);
-            running_sum += block_sum;
+                mbarrier_arrive(p_full0 + 8 * chain);
+            running_sum += sums[0] + sums[1];
         }
-        if (ok)
-            ok = mbarrier_wait(o_full, (blocks - 1) & 1, abort_flag, p.counters, 208);
-        if (ok) {
-            tcgen05_fence_after();
-            const float inverse = 1.f / running_sum;
+        if (ok && mine > 0)
+            ok = mbarrier_wait(o_full0 + 8 * chain, (mine - 1) & 1, abort_flag, p.counters, 208);
+        // merge the two chains: each publishes its reference maximum and sum, then takes half of the
+        // output columns of both accumulators
+        exchange[chain * 2 * BlockM + row] = reference_max;
+        exchange[chain * 2 * BlockM + BlockM + row] = running_sum;
+        tcgen05_fence_before();
+        asm volatile("bar.sync 1, 256;" ::: "memory");
+        tcgen05_fence_after();
+        const int other = chain ^ 1;
+        const float other_max = exchange[other * 2 * BlockM + row], other_sum = exchange[other * 2 * BlockM + BlockM + row];
+        const float top = fmaxf(reference_max, other_max); // chain 0 has seen key 0: never -inf for a valid row
+        const float mine_factor = reference_max == -CUDART_INF_F ? 0.f : fast_exp2((reference_max - top) * p.scale_log2);
+        const float other_factor = other_max == -CUDART_INF_F ? 0.f : fast_exp2((other_max - top) * p.scale_log2);
+        const float total = running_sum * mine_factor + other_sum * other_factor;
+        if (ok && *abort_flag == 0) {
+            const float inverse = 1.f / total;
             uint32_t a[32], c[32];
-            tmem_load_32x32_async(tmem_o + lane_base, a);
-            tmem_load_32x32_async(tmem_o + lane_base + 32, c);
+            // this warp's half of the columns (32 chain .. 32 chain + 31) from its own and the other accumulator;
+            // an accumulator whose chain took no step was never written and is not read
+            const bool other_used = steps > 1 || other == 0;
+            tmem_load_32x32_async(tmem_o + chain * 32, a);
+            if (other_used)
+                tmem_load_32x32_async(tmem_o0 + 64 * other + lanes + chain * 32, c);
             tmem_wait_load(a);
-            tmem_wait_load(c);
+            if (other_used)
+                tmem_wait_load(c);
             if (position < p.context) {
-                bf16 *out = p.out + (int64_t(row0) + position) * p.width + h * HeadSize;
+                bf16 *out = p.out + (int64_t(row0) + position) * p.width + h * HeadSize + chain * 32;
+                const bool mine_used = mine > 0;
 #pragma unroll
-                for (int g = 0; g < HeadSize / 8; ++g) {
+                for (int g = 0; g < 4; ++g) {
                     float v[8];
 #pragma unroll
-                    for (int i = 0; i < 8; ++i)
-                        v[i] = __uint_as_float(g < 4 ? a[g * 8 + i] : c[(g - 4) * 8 + i]) * inverse;
+                    for (int i = 0; i < 8; ++i) {
+                        const float x = mine_used ? __uint_as_float(a[g * 8 + i]) * mine_factor : 0.f;
+                        const float y = other_used ? __uint_as_float(c[g * 8 + i]) * other_factor : 0.f;
+                        v[i] = (x + y) * inverse;
+                    }
                     store8(out + g * 8, v);
                 }
-                // natural-log sum-exp of the scaled scores
-                p.lse[(int64_t(b) * p.heads + h) * p.context + position] =
-                    (reference_max * p.scale_log2 + log2f(running_sum)) * 0.6931471805599453f;
+                if (chain == 0) // natural-log sum-exp of the scaled scores
+                    p.lse[(int64_t(b) * p.heads + h) * p.context + position] =
+                        (top * p.scale_log2 + log2f(total)) * 0.6931471805599453f;
             }
         }
     }
@@ -752,9 +789,10 @@ void launch_flash_attention_forward(const void *qkv, void *out, float *lse, int 
     p.tiles = (context + BlockM - 1) / BlockM;
     p.scale_log2 = 1.4426950408889634f / sqrtf(float(HeadSize));
     p.counters = counters;
-    CUtensorMap map = make_map_bf16(qkv, uint64_t(3) * width, uint64_t(batch) * context, 1, uint64_t(3) * width, 0,
-                                    HeadSize, 128);
-    flash_forward_kernel<<<batch * heads * p.tiles, ForwardThreads, ForwardShared, s>>>(map, p);
+    const uint64_t rows = uint64_t(batch) * context;
+    CUtensorMap map_q = make_map_bf16(qkv, uint64_t(3) * width, rows, 1, uint64_t(3) * width, 0, HeadSize, BlockM);
+    CUtensorMap map_kv = make_map_bf16(qkv, uint64_t(3) * width, rows, 1, uint64_t(3) * width, 0, HeadSize, KeyStep);
+    flash_forward_kernel<<<batch * heads * p.tiles, ForwardThreads, ForwardShared, s>>>(map_q, map_kv, p);
     CHECK_CUDA(cudaGetLastError());
 }
 
