@@ -201,3 +201,19 @@ def test_graph_replay_is_bit_identical_to_direct_launches():
             results.append((first, engine.training_losses(4).copy(), engine.weights()))
     for a, b in zip(*results):
         np.testing.assert_array_equal(a, b)
+
+
+def test_predict_runs_one_sequence_and_matches_the_batched_forward():
+    """tg_predict covers one sequence (the reference replicates the context over the batch and reads
+    the first copy); its logits are those of the batched forward on the replicated context."""
+    depth, width, heads, context, batch = 2, 256, 4, 128, 8
+    arch, model, w, x, _ = fixture(depth, width, heads, context, batch, False)
+    with Native(ConfigEx.gpt(Config(depth=depth, context=context, batch=batch), width, heads)) as engine:
+        engine.set_weights(w)
+        logits = engine.predict(x[0])
+        batched, _, _ = engine.batch(np.repeat(x[:1], batch, 0), np.zeros((batch, context), np.uint8), backward=False)
+        again = engine.predict(x[0])
+    np.testing.assert_array_equal(logits, again)
+    assert relative(logits, batched[0, -1]) <= 2e-3
+    expected = model.batch(x[:1], np.zeros((1, context), np.uint8), False)[0][0, -1]
+    assert relative(logits, expected) <= 1e-2

@@ -151,7 +151,7 @@ void Engine::initialize() {
     allocate(norm_partial, size_t(norm_blocks) * 2 * W, false);
     if (W <= 1024 && tokens >= 4096)
         allocate(embedding_partial, size_t(EmbeddingSlices) * Vocabulary * W, false);
-    sumsq_blocks = sms * 2;
+    sumsq_blocks = sms * 8;
     allocate(sumsq_partial, sumsq_blocks);
 
     // Per 8 parameters: 0 = Muon, 1 = AdamW, 2 = AdamW with decay (reference cuda/optim.cuh:5-15:
@@ -336,7 +336,8 @@ void Engine::set_onecycle(const TgOneCycle &s) {
 // ------------------------------------------------------------------------------- forward -----
 void Engine::forward(bool want_gradient, bool dump_logits) {
     const TgConfigEx &c = config;
-    const int W = c.width, Hd = c.hidden, M = tokens, B = c.base.batch, T = c.base.context, H = c.heads;
+    const int B = forward_batch ? forward_batch : c.base.batch, T = c.base.context, M = B * T;
+    const int W = c.width, Hd = c.hidden, H = c.heads;
     const int depth = c.base.depth;
     const bool layer_norm = c.norm == TG_NORM_LAYER;
     auto norm = [&](const void *in, int64_t scale, int64_t bias, void *out) {
@@ -727,15 +728,22 @@ void Engine::predict(const uint8_t *context, float *logits256) {
     if (!context || !logits256)
         throw std::runtime_error("Missing prediction input or output");
     set_device();
-    const int B = config.base.batch, T = config.base.context;
+    const int T = config.base.context;
     if (!logits_fp32)
         allocate(logits_fp32, size_t(tokens) * Vocabulary, false);
-    std::vector<uint8_t> input(tokens), target(tokens, 0);
-    for (int b = 0; b < B; ++b)
-        std::copy(context, context + T, input.begin() + size_t(b) * T);
-    CHECK_CUDA(cudaMemcpyAsync(x, input.data(), tokens, cudaMemcpyHostToDevice, stream));
-    CHECK_CUDA(cudaMemcpyAsync(y, target.data(), tokens, cudaMemcpyHostToDevice, stream));
-    one_step(RunMode::Evaluate);
+    // One sequence through the forward pass.  The reference fills the whole batch with copies of the
+    // context (cuda/runtime.cu:322-351) and reads row T-1 of the first; sequences are independent, so
+    // the single row gives the same logits for 1/batch of the work.
+    CHECK_CUDA(cudaMemcpyAsync(x, context, T, cudaMemcpyHostToDevice, stream));
+    CHECK_CUDA(cudaMemsetAsync(y, 0, T, stream));
+    forward_batch = 1;
+    try {
+        one_step(RunMode::Evaluate);
+    } catch (...) {
+        forward_batch = 0;
+        throw;
+    }
+    forward_batch = 0;
     CHECK_CUDA(cudaMemcpyAsync(logits256, logits_fp32 + size_t(T - 1) * Vocabulary, Vocabulary * sizeof(float),
                                cudaMemcpyDeviceToHost, stream));
     CHECK_CUDA(cudaStreamSynchronize(stream));

@@ -91,6 +91,7 @@ struct Engine {
     int64_t launches = 0, graph_launches = 0;
     cudaGraphExec_t step_graph = nullptr; // one captured training step
     bool graph_warm = false;
+    int forward_batch = 0; // sequences the next forward pass covers (0: the configured batch)
     uint64_t graph_generation = 0;
     void drop_graph();
 

@@ -12,7 +12,17 @@ __global__ void __launch_bounds__(256) sum_squares_kernel(const float *gradient,
     per = (per + 3) / 4 * 4;
     int64_t begin = blockIdx.x * per, end = begin + per < count ? begin + per : count;
     float sum = 0;
-    for (int64_t i = begin + threadIdx.x * 4; i < end; i += 256 * 4) {
+    int64_t i = begin + threadIdx.x * 4;
+    for (; i + 3 * 1024 + 4 <= end; i += 4 * 1024) { // four independent 128-bit loads in flight per thread
+        float4 g[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+            g[u] = *reinterpret_cast<const float4 *>(gradient + i + u * 1024);
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+            sum += g[u].x * g[u].x + g[u].y * g[u].y + g[u].z * g[u].z + g[u].w * g[u].w;
+    }
+    for (; i < end; i += 256 * 4) {
         if (i + 4 <= end) {
             float4 g = *reinterpret_cast<const float4 *>(gradient + i);
             sum += g.x * g.x + g.y * g.y + g.z * g.z + g.w * g.w;

@@ -16,6 +16,7 @@ from __future__ import annotations
 import argparse
 import json
 
+import numpy as np
 import torch
 
 from . import bridge
@@ -104,6 +105,22 @@ def cross_entropy_case(lib, rows, iters):
     return {"kernel": "cross_entropy", "rows": rows, "us": seconds * 1e6, "gbs": bytes_moved / seconds / 1e9}
 
 
+def predict_case(iters):
+    """Latency of tg_predict on BASELINE config 3 (one 1024-byte context through 12 layers)."""
+    import time
+    base = bridge.Config(depth=12, context=1024, batch=32)
+    context = np.random.default_rng(0).integers(0, 256, 1024, dtype=np.uint8)
+    with bridge.Native(bridge.ConfigEx.gpt(base, 768, 12)) as engine:
+        for _ in range(3):
+            engine.predict(context)
+        start = time.perf_counter()
+        for _ in range(iters):
+            engine.predict(context)
+        seconds = (time.perf_counter() - start) / iters
+    return {"kernel": "predict", "config": "12L-768d-ctx1024", "ms": seconds * 1e3,
+            "note": "host call to host logits, one sequence"}
+
+
 def main() -> None:
     parser = argparse.ArgumentParser()
     parser.add_argument("--only", default="all")
@@ -132,6 +149,8 @@ def main() -> None:
         results.append(attention_case(lib, 32, 1024, 12, args.iters, True))
     if args.only in ("all", "cross_entropy"):
         results.append(cross_entropy_case(lib, tokens, args.iters))
+    if args.only == "predict":
+        results.append(predict_case(args.iters))
     for r in results:
         print(json.dumps(r))
 
