@@ -392,46 +392,90 @@ __global__ void __launch_bounds__(256) norm_backward_reduce_kernel(const float *
             dbias[c - width] = total;
     }
 }
-// Register-resident variant for widths 256..1024: x and dy are read once; each lane keeps the
-// scale/bias gradient sums of its own columns over all rows of its warp, warps are summed in
-// order through shared memory, blocks in order by the reduce kernel: deterministic.
+// Eight elements as they arrive from memory, converted when used: the row fetched ahead of its turn
+// costs half the registers of its FP32 form.
+template <class T> struct Packet;
+template <> struct Packet<bf16> { uint4 u; };
+template <> struct Packet<float> { float4 a, b; };
+__device__ __forceinline__ void fetch8(const bf16 *p, Packet<bf16> &r) { r.u = *reinterpret_cast<const uint4 *>(p); }
+__device__ __forceinline__ void fetch8(const float *p, Packet<float> &r) {
+    r.a = *reinterpret_cast<const float4 *>(p), r.b = *reinterpret_cast<const float4 *>(p + 4);
+}
+__device__ __forceinline__ void unpack8(const Packet<bf16> &r, float (&v)[8]) {
+    const unsigned w[4] = {r.u.x, r.u.y, r.u.z, r.u.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        v[2 * i] = __uint_as_float(w[i] << 16);
+        v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
+}
+__device__ __forceinline__ void unpack8(const Packet<float> &r, float (&v)[8]) {
+    v[0] = r.a.x, v[1] = r.a.y, v[2] = r.a.z, v[3] = r.a.w, v[4] = r.b.x, v[5] = r.b.y, v[6] = r.b.z, v[7] = r.b.w;
+}
+
+// Register-resident variant for widths 256..1024: x, dy and the residual gradient are read once, and
+// a warp fetches its next row while it works on the current one.  Each warp keeps the scale/bias
+// gradient sums of its rows in its own slice of shared memory (a lane owns its columns there);
+// warps are summed in order at the end, blocks in order by the reduce kernel: deterministic.
 template <class T, int V> __global__ void __launch_bounds__(256, 2) norm_backward_rows_kernel(NormBackwardArgs a) {
-    extern __shared__ float sums[]; // [warps][2][width]; first `width` floats hold the scale during the row loop
+    extern __shared__ float sums[]; // [V * 256] scale, then [warps][2][V * 256] gradient sums
     const int lane = threadIdx.x % 32, warp = threadIdx.x / 32, warps = blockDim.x / 32;
-    float dw[V][8], db[V][8];
+    float *scale = sums, *mine = sums + V * 256 + warp * 2 * V * 256;
     for (int c = threadIdx.x; c < V * 256; c += blockDim.x)
-        sums[c] = join_weight(a.scale_high[c], a.scale_low[c]);
+        scale[c] = join_weight(a.scale_high[c], a.scale_low[c]);
+    for (int c = lane; c < 2 * V * 256; c += 32)
+        mine[c] = 0.f;
     __syncthreads();
-#pragma unroll
-    for (int v = 0; v < V; ++v)
-#pragma unroll
-        for (int j = 0; j < 8; ++j)
-            dw[v][j] = db[v][j] = 0.f;
-    for (int row = blockIdx.x * warps + warp; row < a.rows; row += gridDim.x * warps) {
+    const bool residual = a.residual_in != nullptr;
+    const int stride = gridDim.x * warps;
+    Packet<T> nx[V], ng[V], nr[V];
+    auto fetch = [&](int row) {
         const int64_t offset = int64_t(row) * a.width;
-        float x[V][8], g[V][8];
 #pragma unroll
         for (int v = 0; v < V; ++v) {
-            load8((const T *)a.x + offset + (v * 32 + lane) * 8, x[v]);
-            load8((const T *)a.dy + offset + (v * 32 + lane) * 8, g[v]);
+            fetch8((const T *)a.x + offset + (v * 32 + lane) * 8, nx[v]);
+            fetch8((const T *)a.dy + offset + (v * 32 + lane) * 8, ng[v]);
+            if (residual)
+                fetch8((const T *)a.residual_in + offset + (v * 32 + lane) * 8, nr[v]);
         }
+    };
+    int row = blockIdx.x * warps + warp;
+    if (row < a.rows)
+        fetch(row);
+    for (; row < a.rows; row += stride) {
+        const int64_t offset = int64_t(row) * a.width;
+        float x[V][8], g[V][8];
+        Packet<T> r[V];
+#pragma unroll
+        for (int v = 0; v < V; ++v) {
+            unpack8(nx[v], x[v]);
+            unpack8(ng[v], g[v]);
+            r[v] = nr[v];
+        }
+        if (row + stride < a.rows)
+            fetch(row + stride); // in flight during this row's arithmetic
         float mean, inv;
         row_moments<V>(a.kind, x, a.width, mean, inv);
         float part_dz[4] = {0, 0, 0, 0}, part_dzz[4] = {0, 0, 0, 0};
 #pragma unroll
         for (int v = 0; v < V; ++v) {
-            float w[8];
-            load8(sums + (v * 32 + lane) * 8, w);
+            float w[8], dw[8], db[8];
+            float *slot = mine + (v * 32 + lane) * 8;
+            load8(scale + (v * 32 + lane) * 8, w);
+            load8(slot, dw);
+            load8(slot + V * 256, db);
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
                 const float z = (x[v][j] - mean) * inv, dz = g[v][j] * w[j];
                 x[v][j] = z; // keep the normalised value
                 part_dz[j % 4] += dz;
                 part_dzz[j % 4] += dz * z;
-                dw[v][j] += g[v][j] * z;
-                db[v][j] += g[v][j];
+                dw[j] += g[v][j] * z;
+                db[j] += g[v][j];
                 g[v][j] = dz; // keep dy * scale
             }
+            store8(slot, dw);
+            store8(slot + V * 256, db);
         }
         const float sum_dzz = warp_sum((part_dzz[0] + part_dzz[1]) + (part_dzz[2] + part_dzz[3])) / a.width;
         const float sum_dz =
@@ -442,38 +486,35 @@ template <class T, int V> __global__ void __launch_bounds__(256, 2) norm_backwar
 #pragma unroll
             for (int j = 0; j < 8; ++j)
                 out[j] = (g[v][j] - sum_dz - x[v][j] * sum_dzz) * inv;
-            if (a.residual_in) {
-                float r[8];
-                load8((const T *)a.residual_in + offset + (v * 32 + lane) * 8, r);
+            if (residual) {
+                float res[8];
+                unpack8(r[v], res);
 #pragma unroll
                 for (int j = 0; j < 8; ++j)
-                    out[j] = r[j] + rounded<T>(out[j]);
+                    out[j] = res[j] + rounded<T>(out[j]);
             }
             store8((T *)a.dx + offset + (v * 32 + lane) * 8, out);
         }
     }
-    __syncthreads(); // every warp is done reading the scale
-#pragma unroll
-    for (int v = 0; v < V; ++v)
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            const int c = (v * 32 + lane) * 8 + j;
-            sums[(warp * 2) * a.width + c] = dw[v][j];
-            sums[(warp * 2 + 1) * a.width + c] = db[v][j];
-        }
     __syncthreads();
     for (int c = threadIdx.x; c < 2 * a.width; c += blockDim.x) {
         float total = 0;
         for (int k = 0; k < warps; ++k)
-            total += sums[k * 2 * a.width + c];
+            total += sums[V * 256 + k * 2 * a.width + c];
         a.partial[int64_t(blockIdx.x) * 2 * a.width + c] = total;
     }
 }
 template <class T, int V> static void launch_norm_backward_rows(const NormBackwardArgs &a, cudaStream_t s) {
-    const size_t shared = size_t(8) * 2 * a.width * sizeof(float);
-    if (shared > 48 * 1024)
+    const size_t shared = size_t(V * 256 + 8 * 2 * a.width) * sizeof(float);
+    static unsigned long long configured = 0; // one bit per device; this instantiation's own
+    int device = 0;
+    CHECK_CUDA(cudaGetDevice(&device));
+    if (shared > 48 * 1024 && (device >= 64 || !(configured >> device & 1))) {
         CHECK_CUDA(cudaFuncSetAttribute(norm_backward_rows_kernel<T, V>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                         int(shared)));
+        if (device < 64)
+            configured |= 1ull << device;
+    }
     norm_backward_rows_kernel<T, V><<<a.blocks, 256, shared, s>>>(a);
 }
 int norm_backward_blocks(int rows, int sms) {
