@@ -22,6 +22,7 @@
 // atomic ticket, no spinning) sums the partials in split order, so results are deterministic.
 #include "device_utils.cuh"
 #include "sm100.cuh"
+#include <cstdio>
 #include <cstdlib>
 #include <atomic>
 #include <mutex>
@@ -644,6 +645,10 @@ void launch_gemm_tc(const GemmArgs &g, int sms, StepCounters *counters, cudaStre
             }
         }
     }
+    static const bool trace = getenv("TURBOGPT_GEMM_TRACE") != nullptr; // prints every schedule chosen
+    if (trace)
+        fprintf(stderr, "gemm %d x %d x %d batch %d a_mn %d b_mn %d epilogue %d: bn %d splits %d pair %d\n", g.m, g.n,
+                g.k, g.batch, p.a_mn, p.b_mn, p.epilogue, p.bn, p.splits, pair);
     const int unit = pair ? 2 : 1;
     const int padded_m_tiles = (m_tiles + unit - 1) / unit * unit;
     const int n_tiles = (g.n + p.bn - 1) / p.bn;
