@@ -217,3 +217,18 @@ def test_predict_runs_one_sequence_and_matches_the_batched_forward():
     assert relative(logits, batched[0, -1]) <= 2e-3
     expected = model.batch(x[:1], np.zeros((1, context), np.uint8), False)[0][0, -1]
     assert relative(logits, expected) <= 1e-2
+
+
+@pytest.mark.parametrize("context,batch", [(200, 3), (72, 5)])
+def test_ragged_context_on_the_tensor_core_path(context, batch):
+    """Contexts off the 128-row attention tile and the 64-key step, odd batch, head size 64 (the tcgen05
+    attention and GEMM kernels run): BF16 engine against the BF16 CPU oracle."""
+    depth, width, heads = 2, 256, 4
+    arch, model, w, x, y = fixture(depth, width, heads, context, batch, False)
+    target, expected_grad, expected_losses = model.batch(x, y)
+    with Native(ConfigEx.gpt(Config(depth=depth, context=context, batch=batch, clip=0), width, heads)) as engine:
+        engine.set_weights(w)
+        logits, gradients, losses = engine.batch(x, y)
+    assert relative(logits, target) <= 1e-2
+    assert relative(gradients, expected_grad) <= 1e-2
+    np.testing.assert_allclose(losses, expected_losses, rtol=1e-2, atol=1e-2)
