@@ -329,8 +329,10 @@ constexpr int DqShared = 2 * TileBytes + Ring * 2 * StepBytes + 1024 + 256; // Q
 constexpr int DkvShared = 2 * TileBytes + Ring * 2 * StepBytes + Ring * 64 * 4 + 1024 + 256; // + statistics
 
 struct BackwardParams {
+    const bf16 *out; // forward output, for delta = rowsum(dO * O)
     bf16 *dqkv;
-    const float *lse, *delta;
+    const float *lse;
+    float *delta;    // written by the dq kernel, read by the dk/dv kernel that follows it
     int batch, context, heads, width, tiles;
     float scale, scale_log2;
     StepCounters *counters;
@@ -480,10 +482,36 @@ flash_dq_kernel(const __grid_constant__ CUtensorMap map_qkv128, const __grid_con
         const bool valid = position < p.context, ragged = warp_first + 31 >= p.context;
         const int64_t stat = (int64_t(b) * p.heads + h) * p.context + position;
         const float lse2 = valid ? p.lse[stat] * 1.4426950408889634f : 0.f;
-        const float delta = valid ? p.delta[stat] : 0.f;
+        // delta = rowsum(dO * O) for this thread's query: O from global memory, dO from the tile the TMA
+        // warp loaded (row r of a 128-byte-swizzled tile keeps its 16-byte chunk c at position c ^ (r % 8)).
+        float delta = 0.f;
         bool ok = true;
+        {
+            uint4 o[8];
+            if (valid) {
+                const uint4 *source = reinterpret_cast<const uint4 *>(p.out + (int64_t(row0) + position) * p.width + h * HeadSize);
+#pragma unroll
+                for (int c = 0; c < 8; ++c)
+                    o[c] = source[c];
+            }
+            ok = mbarrier_wait(qdo_full, 0, abort_flag, p.counters, 308);
+            if (ok && valid) {
+                const uint4 *tile_row = reinterpret_cast<const uint4 *>(aligned + TileBytes + row * 128);
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                    const uint4 g = tile_row[c ^ (row & 7)];
+                    const unsigned a4[4] = {o[c].x, o[c].y, o[c].z, o[c].w}, b4[4] = {g.x, g.y, g.z, g.w};
+#pragma unroll
+                    for (int i = 0; i < 4; ++i)
+                        delta += __uint_as_float(a4[i] << 16) * __uint_as_float(b4[i] << 16) +
+                                 __uint_as_float(a4[i] & 0xffff0000u) * __uint_as_float(b4[i] & 0xffff0000u);
+                }
+                if (half == 0)
+                    p.delta[stat] = delta;
+            }
+        }
         int stage = 0, phase = 0;
-        for (int j = 0; j < blocks; ++j) {
+        for (int j = 0; j < blocks && ok; ++j) {
             ok = mbarrier_wait(s_full0 + 8 * stage, phase, abort_flag, p.counters, 305);
             if (!ok)
                 break;
@@ -796,9 +824,9 @@ void launch_flash_attention_forward(const void *qkv, void *out, float *lse, int 
     CHECK_CUDA(cudaGetLastError());
 }
 
-void launch_flash_attention_backward(const void *qkv, const void *dout, const float *lse, const float *delta,
-                                     void *dqkv, int batch, int context, int heads, StepCounters *counters,
-                                     cudaStream_t s) {
+void launch_flash_attention_backward(const void *qkv, const void *out, const void *dout, const float *lse,
+                                     float *delta, void *dqkv, int batch, int context, int heads,
+                                     StepCounters *counters, cudaStream_t s) {
     static bool configured[64] = {};
     int device = 0;
     CHECK_CUDA(cudaGetDevice(&device));
@@ -809,7 +837,7 @@ void launch_flash_attention_backward(const void *qkv, const void *dout, const fl
     }
     const int width = heads * HeadSize;
     BackwardParams p{};
-    p.dqkv = static_cast<bf16 *>(dqkv), p.lse = lse, p.delta = delta;
+    p.out = static_cast<const bf16 *>(out), p.dqkv = static_cast<bf16 *>(dqkv), p.lse = lse, p.delta = delta;
     p.batch = batch, p.context = context, p.heads = heads, p.width = width;
     p.tiles = (context + BlockM - 1) / BlockM;
     p.scale = 1.f / sqrtf(float(HeadSize));
@@ -821,7 +849,7 @@ void launch_flash_attention_backward(const void *qkv, const void *dout, const fl
     CUtensorMap do128 = make_map_bf16(dout, width, rows, 1, width, 0, HeadSize, 128);
     CUtensorMap do32 = make_map_bf16(dout, width, rows, 1, width, 0, HeadSize, Step);
     const int grid = batch * heads * p.tiles;
+    flash_dq_kernel<<<grid, BackwardThreads, DqShared, s>>>(qkv128, qkv32, do128, p); // also writes delta
     flash_dkv_kernel<<<grid, BackwardThreads, DkvShared, s>>>(qkv128, qkv32, do32, p);
-    flash_dq_kernel<<<grid, BackwardThreads, DqShared, s>>>(qkv128, qkv32, do128, p);
     CHECK_CUDA(cudaGetLastError());
 }

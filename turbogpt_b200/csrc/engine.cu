@@ -492,9 +492,8 @@ void Engine::backward() {
             SoftmaxAttentionBackwardArgs at{a.qkv, a.attended, dbranch, a.lse, attention_scratch, dqkv, B, T, W, H};
             run(FAttentionBackward, [&] {
                 if (tensor_cores && act == Dtype::BF16 && flash_attention_supported(W, H)) {
-                    launch_attention_delta(act, at, stream);
-                    launch_flash_attention_backward(a.qkv, dbranch, a.lse, attention_scratch, dqkv, B, T, H, counters,
-                                                    stream);
+                    launch_flash_attention_backward(a.qkv, a.attended, dbranch, a.lse, attention_scratch, dqkv, B, T, H,
+                                                    counters, stream);
                 } else {
                     launch_softmax_attention_backward(act, at, stream);
                 }

@@ -290,8 +290,7 @@ int tg_ex_attention_backward(const void *qkv, const void *out, const void *dout,
                                    static_cast<cudaStream_t>(stream)));
         SoftmaxAttentionBackwardArgs a{qkv, out, dout, lse, delta, dqkv, batch, context, heads * d_head, heads};
         if (tensor_cores) {
-            launch_attention_delta(Dtype::BF16, a, static_cast<cudaStream_t>(stream));
-            launch_flash_attention_backward(qkv, dout, lse, delta, dqkv, batch, context, heads, nullptr,
+            launch_flash_attention_backward(qkv, out, dout, lse, delta, dqkv, batch, context, heads, nullptr,
                                             static_cast<cudaStream_t>(stream));
         } else {
             launch_softmax_attention_backward(Dtype::BF16, a, static_cast<cudaStream_t>(stream));
