@@ -172,25 +172,61 @@ flash_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
             tcgen05_fence_after();
             const int key0 = j * KeyStep;
             const bool diagonal = key0 + KeyStep - 1 > warp_first; // some key of the step lies after some query of the warp
-            float block_max = -CUDART_INF_F;
-            { // first pass over the scores: the row maximum
-                uint32_t s0[32], s1[32];
-                tmem_load_32x32_async(tmem_s, s0);
-                tmem_load_32x32_async(tmem_s + 32, s1);
-                tmem_wait_load(s0);
-                tmem_wait_load(s1);
-                if (diagonal) {
+            if (mine > 0 && !diagonal) {
+                // One pass: exponentials against the reference maximum this chain already has, the row
+                // maximum tracked on the side.  That is exact as long as no row's maximum has grown by
+                // more than 2^8; if one has, nothing has been written yet and the step is redone below.
+                const float offset = reference_max * p.scale_log2;
+                uint32_t packed[32];
+                float m0 = -CUDART_INF_F, m1 = -CUDART_INF_F, sum0 = 0.f, sum1 = 0.f;
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        if (key0 + i > position) s0[i] = 0xff800000u;
-                        if (key0 + 32 + i > position) s1[i] = 0xff800000u;
+                for (int part = 0; part < 4; ++part) { // 16 keys at a time
+                    uint32_t s[16];
+                    tmem_load_32x16_async(tmem_s + part * 16, s);
+                    tmem_wait_load(s);
+#pragma unroll
+                    for (int i = 0; i < 16; i += 2) {
+                        const float x0 = __uint_as_float(s[i]), x1 = __uint_as_float(s[i + 1]);
+                        m0 = fmaxf(m0, x0);
+                        m1 = fmaxf(m1, x1);
+                        const float p0 = fast_exp2(fmaf(x0, p.scale_log2, -offset));
+                        const float p1 = fast_exp2(fmaf(x1, p.scale_log2, -offset));
+                        sum0 += p0;
+                        sum1 += p1;
+                        packed[part * 8 + i / 2] = pack_bf16(p0, p1);
                     }
                 }
+                const bool fits = (fmaxf(m0, m1) - reference_max) * p.scale_log2 <= 8.f; // false for a -inf reference
+                if (__all_sync(0xffffffffu, fits)) {
+                    tmem_store_32x32(tmem_s, packed);
+                    tmem_wait_store();
+                    tcgen05_fence_before();
+                    __syncwarp();
+                    if (lane == 0)
+                        mbarrier_arrive(p_full0 + 8 * chain);
+                    running_sum += sum0 + sum1;
+                    continue;
+                }
+            }
+            float block_max = -CUDART_INF_F;
+            { // first pass over the scores: the row maximum, 32 keys at a time
                 float m0 = -CUDART_INF_F, m1 = -CUDART_INF_F;
 #pragma unroll
-                for (int i = 0; i < 32; i += 2) {
-                    m0 = fmaxf(m0, fmaxf(__uint_as_float(s0[i]), __uint_as_float(s1[i])));
-                    m1 = fmaxf(m1, fmaxf(__uint_as_float(s0[i + 1]), __uint_as_float(s1[i + 1])));
+                for (int half = 0; half < 2; ++half) {
+                    uint32_t s[32];
+                    tmem_load_32x32_async(tmem_s + half * 32, s);
+                    tmem_wait_load(s);
+                    if (diagonal) {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i)
+                            if (key0 + half * 32 + i > position)
+                                s[i] = 0xff800000u;
+                    }
+#pragma unroll
+                    for (int i = 0; i < 32; i += 2) {
+                        m0 = fmaxf(m0, __uint_as_float(s[i]));
+                        m1 = fmaxf(m1, __uint_as_float(s[i + 1]));
+                    }
                 }
                 block_max = fmaxf(m0, m1);
             }
