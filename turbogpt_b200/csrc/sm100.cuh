@@ -88,10 +88,12 @@ __device__ __forceinline__ void mbarrier_arrive(uint32_t bar) {
 }
 __device__ __forceinline__ bool mbarrier_try_wait(uint32_t bar, uint32_t parity) {
     uint32_t done;
-    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+    // The third operand lets the hardware park the thread for up to that many nanoseconds while the
+    // phase is incomplete (it is woken when the phase completes): fewer polls from idle warps.
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
                  "selp.u32 %0, 1, 0, p;\n\t}"
                  : "=r"(done)
-                 : "r"(bar), "r"(parity)
+                 : "r"(bar), "r"(parity), "r"(100000u)
                  : "memory");
     return done != 0;
 }
