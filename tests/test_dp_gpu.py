@@ -22,13 +22,13 @@ def _fixture():
     return weights, data
 
 
-def _rank(rank, world, ident, out):
+def _rank(rank, world, ident, flags, out):
     import os
     os.environ["NCCL_NVLS_ENABLE"] = "0"
     weights, data = _fixture()
     base = Config(depth=SHAPE["depth"], context=SHAPE["context"], batch=BATCH, device=rank, learning_rate=1e-3,
                   clip=1.0)
-    ex = ConfigEx.gpt(base, SHAPE["width"], SHAPE["heads"], world=world, rank=rank)
+    ex = ConfigEx.gpt(base, SHAPE["width"], SHAPE["heads"], world=world, rank=rank, flags=flags)
     C.memmove(ex.nccl_id, ident, 128)
     with Native(ex) as engine:
         engine.set_weights(weights)
@@ -39,14 +39,16 @@ def _rank(rank, world, ident, out):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_two_ranks_follow_one_engine_with_the_global_batch():
+@pytest.mark.parametrize("flags", [0, bridge.FLAG_BF16_GRADIENT_EXCHANGE])
+def test_two_ranks_follow_one_engine_with_the_global_batch(flags):
+    """FP32 gradient buckets (the default) and buckets cast to BF16 for the wire."""
     import torch.multiprocessing as mp
     lib = bridge.load_library()
     ident = (C.c_uint8 * 128)()
     assert lib.tg_ex_nccl_unique_id(ident) == 0, lib.tg_error()
     ctx = mp.get_context("spawn")
     out = ctx.Queue()
-    procs = [ctx.Process(target=_rank, args=(r, 2, bytes(ident), out)) for r in range(2)]
+    procs = [ctx.Process(target=_rank, args=(r, 2, bytes(ident), flags, out)) for r in range(2)]
     for p in procs:
         p.start()
     results = dict()
