@@ -233,6 +233,27 @@ template <class T> __global__ void __launch_bounds__(256) norm_kernel(NormArgs a
         store8(y + c, out);
     }
 }
+// Eight elements as they arrive from memory, converted when used: the row fetched ahead of its turn
+// costs half the registers of its FP32 form.
+template <class T> struct Packet;
+template <> struct Packet<bf16> { uint4 u; };
+template <> struct Packet<float> { float4 a, b; };
+__device__ __forceinline__ void fetch8(const bf16 *p, Packet<bf16> &r) { r.u = *reinterpret_cast<const uint4 *>(p); }
+__device__ __forceinline__ void fetch8(const float *p, Packet<float> &r) {
+    r.a = *reinterpret_cast<const float4 *>(p), r.b = *reinterpret_cast<const float4 *>(p + 4);
+}
+__device__ __forceinline__ void unpack8(const Packet<bf16> &r, float (&v)[8]) {
+    const unsigned w[4] = {r.u.x, r.u.y, r.u.z, r.u.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        v[2 * i] = __uint_as_float(w[i] << 16);
+        v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
+}
+__device__ __forceinline__ void unpack8(const Packet<float> &r, float (&v)[8]) {
+    v[0] = r.a.x, v[1] = r.a.y, v[2] = r.a.z, v[3] = r.a.w, v[4] = r.b.x, v[5] = r.b.y, v[6] = r.b.z, v[7] = r.b.w;
+}
+
 // Widths of 256..1024 in steps of 256: the row lives in registers (one 128-bit load per 256
 // columns and lane), so x is read once; scale and bias are read once per thread.
 template <int V> __device__ __forceinline__ void row_moments(int kind, const float (&x)[V][8], int width,
@@ -268,13 +289,23 @@ template <class T, int V> __global__ void __launch_bounds__(256, 4) norm_rows_ke
         sb[c] = a.kind == TG_NORM_LAYER ? join_weight(a.bias_high[c], a.bias_low[c]) : 0.f;
     }
     __syncthreads();
-    for (int row = blockIdx.x * warps + threadIdx.x / 32; row < a.rows; row += gridDim.x * warps) {
-        const T *x = (const T *)a.x + int64_t(row) * a.width;
+    const int stride = gridDim.x * warps;
+    int row = blockIdx.x * warps + threadIdx.x / 32;
+    Packet<T> next[V]; // the warp's next row, fetched while the current one is normalised
+    if (row < a.rows)
+#pragma unroll
+        for (int k = 0; k < V; ++k)
+            fetch8((const T *)a.x + int64_t(row) * a.width + (k * 32 + lane) * 8, next[k]);
+    for (; row < a.rows; row += stride) {
         T *y = (T *)a.y + int64_t(row) * a.width;
         float v[V][8];
 #pragma unroll
         for (int k = 0; k < V; ++k)
-            load8(x + (k * 32 + lane) * 8, v[k]);
+            unpack8(next[k], v[k]);
+        if (row + stride < a.rows)
+#pragma unroll
+            for (int k = 0; k < V; ++k)
+                fetch8((const T *)a.x + int64_t(row + stride) * a.width + (k * 32 + lane) * 8, next[k]);
         float mean, inv;
         row_moments<V>(a.kind, v, a.width, mean, inv);
 #pragma unroll
@@ -392,27 +423,6 @@ __global__ void __launch_bounds__(256) norm_backward_reduce_kernel(const float *
             dbias[c - width] = total;
     }
 }
-// Eight elements as they arrive from memory, converted when used: the row fetched ahead of its turn
-// costs half the registers of its FP32 form.
-template <class T> struct Packet;
-template <> struct Packet<bf16> { uint4 u; };
-template <> struct Packet<float> { float4 a, b; };
-__device__ __forceinline__ void fetch8(const bf16 *p, Packet<bf16> &r) { r.u = *reinterpret_cast<const uint4 *>(p); }
-__device__ __forceinline__ void fetch8(const float *p, Packet<float> &r) {
-    r.a = *reinterpret_cast<const float4 *>(p), r.b = *reinterpret_cast<const float4 *>(p + 4);
-}
-__device__ __forceinline__ void unpack8(const Packet<bf16> &r, float (&v)[8]) {
-    const unsigned w[4] = {r.u.x, r.u.y, r.u.z, r.u.w};
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        v[2 * i] = __uint_as_float(w[i] << 16);
-        v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
-    }
-}
-__device__ __forceinline__ void unpack8(const Packet<float> &r, float (&v)[8]) {
-    v[0] = r.a.x, v[1] = r.a.y, v[2] = r.a.z, v[3] = r.a.w, v[4] = r.b.x, v[5] = r.b.y, v[6] = r.b.z, v[7] = r.b.w;
-}
-
 // Register-resident variant for widths 256..1024: x, dy and the residual gradient are read once, and
 // a warp fetches its next row while it works on the current one.  Each warp keeps the scale/bias
 // gradient sums of its rows in its own slice of shared memory (a lane owns its columns there);
