@@ -343,25 +343,24 @@ flash_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
 
 // ------------------------------------------------------------------------------------------
 // Backward.  Two kernels, both deterministic (no atomics):
-//   dq kernel    : one CTA per 128 query rows, stepping over keys 32 at a time.  S = Q K^T and
+//   dq kernel    : one CTA per 128 query rows, stepping over keys 64 at a time.  S = Q K^T and
 //                  dP = dO V^T land in tensor memory; thread = query row computes
 //                  dS = P (dP - delta) with P = exp(S / sqrt(d) - lse), packs it to BF16 over S,
 //                  and dQ += dS K accumulates in tensor memory; 1 / sqrt(d) is applied once at the end.
+//                  It also computes delta = rowsum(dO * O) and leaves it for the second kernel.
 //   dk/dv kernel : one CTA per 128 keys, stepping over queries 32 at a time with everything
 //                  transposed (S^T = K Q^T, dP^T = V dO^T: thread = key row), so P^T and dS^T are
 //                  A operands in tensor memory for dV += P^T dO and dK += dS^T Q.
-// Both are software pipelines: the score buffers are ring-buffered in tensor memory (three deep in
-// the dq kernel, two in the dk/dv kernel), and the MMA thread issues the score products two steps
-// ahead of the accumulation products, so the tensor pipe works on steps j-1 and j+1 while the
-// compute warps turn step j's scores into dS.  256 TMEM columns and under 80 KB of shared memory
-// per CTA: two CTAs share an SM.
+// Both are software pipelines: score buffers are double-buffered in tensor memory and the MMA thread
+// issues the score products ahead of the accumulating products, so the tensor pipe works on the
+// neighbouring steps while the compute warps turn one step's scores into dS.  256 TMEM columns and
+// under 100 KB of shared memory per CTA: two CTAs share an SM.
 // ------------------------------------------------------------------------------------------
 constexpr int BackwardThreads = 320, BackwardTmemColumns = 256; // warp 0 TMA, warp 1 MMA, 8 compute warps
 constexpr int Step = 32;                                        // keys (dq) or queries (dk/dv) per pipeline step
 constexpr int StepBytes = Step * HeadSize * 2;                  // 4 KB: one K, V, Q or dO block
 constexpr int Ring = 4;                                         // shared-memory ring of operand blocks
-constexpr int DqStages = 3, DkvStages = 2;                      // score buffers in tensor memory
-constexpr int DqShared = 2 * TileBytes + Ring * 2 * StepBytes + 1024 + 256; // Q, dO + ring of (K, V)
+constexpr int DkvStages = 2;                                    // score buffers in tensor memory (dk/dv kernel)
 constexpr int DkvShared = 2 * TileBytes + Ring * 2 * StepBytes + Ring * 64 * 4 + 1024 + 256; // + statistics
 
 struct BackwardParams {
@@ -391,17 +390,25 @@ __device__ __forceinline__ void store_accumulator(uint32_t address, bf16 *out, f
     }
 }
 
+// dq kernel.  64 keys per step.  S = Q K^T is double-buffered in tensor memory and issued two steps
+// ahead, so a step's exponentials (the long, SFU-bound part) run while the MMA thread is still
+// issuing the previous step's dQ product and this step's dP = dO V^T; dP has one buffer and is only
+// needed for the final multiply.  Twelve MMAs per 64 keys (4 S, 4 dP, 4 dQ) keep the issuing thread,
+// which pays 40-80 clocks per small MMA, off the critical path.
+constexpr int DqStep = 64, DqStepBytes = DqStep * HeadSize * 2, DqRing = 4;
+constexpr int DqShared = 2 * TileBytes + DqRing * 2 * DqStepBytes + 1024 + 256; // Q, dO + ring of (K, V)
+
 __global__ void __launch_bounds__(BackwardThreads, 2)
-flash_dq_kernel(const __grid_constant__ CUtensorMap map_qkv128, const __grid_constant__ CUtensorMap map_qkv32,
+flash_dq_kernel(const __grid_constant__ CUtensorMap map_qkv128, const __grid_constant__ CUtensorMap map_qkv64,
                 const __grid_constant__ CUtensorMap map_do128, BackwardParams p) {
     extern __shared__ uint8_t raw_shared[];
     const uint32_t base = (smem_address(raw_shared) + 1023u) & ~1023u;
     uint8_t *aligned = raw_shared + (base - smem_address(raw_shared));
-    uint64_t *barriers = reinterpret_cast<uint64_t *>(aligned + 2 * TileBytes + Ring * 2 * StepBytes);
-    const uint32_t qdo_full = smem_address(barriers), kv_full0 = qdo_full + 8, kv_empty0 = kv_full0 + 8 * Ring,
-                   s_full0 = kv_empty0 + 8 * Ring, ds_full0 = s_full0 + 8 * DqStages,
-                   dq_done = ds_full0 + 8 * DqStages; // 2 + 2 Ring + 2 DqStages = 16 barriers
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(barriers + 2 + 2 * Ring + 2 * DqStages);
+    uint64_t *barriers = reinterpret_cast<uint64_t *>(aligned + 2 * TileBytes + DqRing * 2 * DqStepBytes);
+    const uint32_t qdo_full = smem_address(barriers), kv_full0 = qdo_full + 8, kv_empty0 = kv_full0 + 8 * DqRing,
+                   s_full0 = kv_empty0 + 8 * DqRing, ds_full0 = s_full0 + 16, dp_full = ds_full0 + 16,
+                   dq_done = dp_full + 8; // 1 + 2 DqRing + 2 + 2 + 1 + 1 = 15 barriers
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(barriers + 7 + 2 * DqRing);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
     const uint32_t smem_q = base, smem_do = base + TileBytes, smem_kv = base + 2 * TileBytes;
 
@@ -411,18 +418,19 @@ flash_dq_kernel(const __grid_constant__ CUtensorMap map_qkv128, const __grid_con
     const int bh = blockIdx.x % pairs, b = bh / p.heads, h = bh % p.heads;
     const int row0 = b * p.context;
     const int last_key = min(p.context, (tile + 1) * BlockM); // keys 0..last_key-1 can be attended
-    const int blocks = (last_key + Step - 1) / Step;
+    const int blocks = (last_key + DqStep - 1) / DqStep;
 
     if (threadIdx.x == 0) {
         mbarrier_init(qdo_full, 1);
-        for (int s = 0; s < Ring; ++s) {
+        for (int s = 0; s < DqRing; ++s) {
             mbarrier_init(kv_full0 + 8 * s, 1);
             mbarrier_init(kv_empty0 + 8 * s, 1);
         }
-        for (int s = 0; s < DqStages; ++s) {
+        for (int s = 0; s < 2; ++s) {
             mbarrier_init(s_full0 + 8 * s, 1);
             mbarrier_init(ds_full0 + 8 * s, 8);
         }
+        mbarrier_init(dp_full, 1);
         mbarrier_init(dq_done, 1);
         *abort_flag = 0;
         fence_barrier_init();
@@ -435,8 +443,8 @@ flash_dq_kernel(const __grid_constant__ CUtensorMap map_qkv128, const __grid_con
     __syncthreads();
     tcgen05_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    // stage s: S at 64 s (dS packs into columns 0-7 and 16-23 of it), dP at 64 s + 32; dQ at 192
-    const uint32_t tmem_dq = tmem_base + 64 * DqStages;
+    // S buffers at 0 and 64 (a half's packed dS goes to the first 16 columns of its own 32), dP at 128, dQ at 192
+    const uint32_t tmem_dp = tmem_base + 128, tmem_dq = tmem_base + 192;
 
     if (warp == 0) {
         if (elect_one()) {
@@ -444,73 +452,72 @@ flash_dq_kernel(const __grid_constant__ CUtensorMap map_qkv128, const __grid_con
             tma_load_3d(smem_q, &map_qkv128, h * HeadSize, row0 + tile * BlockM, 0, qdo_full);
             tma_load_3d(smem_do, &map_do128, h * HeadSize, row0 + tile * BlockM, 0, qdo_full);
             for (int j = 0; j < blocks; ++j) {
-                const int ring = j % Ring;
-                if (!mbarrier_wait(kv_empty0 + 8 * ring, ((j / Ring) & 1) ^ 1, abort_flag, p.counters, 301))
+                const int ring = j % DqRing;
+                if (!mbarrier_wait(kv_empty0 + 8 * ring, ((j / DqRing) & 1) ^ 1, abort_flag, p.counters, 301))
                     break;
-                const uint32_t bar = kv_full0 + 8 * ring, dst = smem_kv + ring * 2 * StepBytes;
-                mbarrier_expect_tx(bar, 2 * StepBytes);
-                tma_load_3d(dst, &map_qkv32, p.width + h * HeadSize, row0 + j * Step, 0, bar);
-                tma_load_3d(dst + StepBytes, &map_qkv32, 2 * p.width + h * HeadSize, row0 + j * Step, 0, bar);
+                const uint32_t bar = kv_full0 + 8 * ring, dst = smem_kv + ring * 2 * DqStepBytes;
+                mbarrier_expect_tx(bar, 2 * DqStepBytes);
+                tma_load_3d(dst, &map_qkv64, p.width + h * HeadSize, row0 + j * DqStep, 0, bar);
+                tma_load_3d(dst + DqStepBytes, &map_qkv64, 2 * p.width + h * HeadSize, row0 + j * DqStep, 0, bar);
             }
         }
     } else if (warp == 1) {
         if (elect_one()) {
-            const uint32_t idesc_s = instruction_descriptor(BlockM, Step, 0, 0);
+            const uint32_t idesc_s = instruction_descriptor(BlockM, DqStep, 0, 0);
             const uint32_t idesc_dq = instruction_descriptor(BlockM, HeadSize, 0, 1);
             // descriptors are built once; every MMA below only offsets them
             const uint64_t q_desc = smem_descriptor(smem_q, 16, 1024), do_desc = smem_descriptor(smem_do, 16, 1024),
                            kv_desc = smem_descriptor(smem_kv, 16, 1024), k_mn_desc = smem_descriptor(smem_kv, 8192, 1024);
             bool ok = mbarrier_wait(qdo_full, 0, abort_flag, p.counters, 302);
-            int issued = 0, stage_in = 0; // score products issued so far, and the stage the next one fills
-            auto issue_scores = [&]() {
-                const int ring = issued % Ring;
-                ok = mbarrier_wait(kv_full0 + 8 * ring, (issued / Ring) & 1, abort_flag, p.counters, 303);
+            auto issue_s = [&](int j) { // S = Q K_j^T into buffer j % 2; also the first use of ring slot j
+                const int ring = j % DqRing;
+                ok = mbarrier_wait(kv_full0 + 8 * ring, (j / DqRing) & 1, abort_flag, p.counters, 303);
                 if (!ok)
                     return;
                 tcgen05_fence_after();
-                const uint32_t t = tmem_base + 64 * stage_in;
-                const uint64_t k_desc = descriptor_at(kv_desc, ring * 2 * StepBytes),
-                               v_desc = descriptor_at(k_desc, StepBytes);
+                const uint64_t k_desc = descriptor_at(kv_desc, ring * 2 * DqStepBytes);
 #pragma unroll
                 for (int ks = 0; ks < HeadSize / 16; ++ks)
-                    tcgen05_mma_bf16(t, descriptor_at(q_desc, ks * 32), descriptor_at(k_desc, ks * 32), idesc_s, ks > 0);
+                    tcgen05_mma_bf16(tmem_base + 64 * (j & 1), descriptor_at(q_desc, ks * 32),
+                                     descriptor_at(k_desc, ks * 32), idesc_s, ks > 0);
+                tcgen05_commit(s_full0 + 8 * (j & 1));
+            };
+            auto issue_dp = [&](int j) { // dP = dO V_j^T (the slot was awaited by issue_s(j))
+                const uint64_t v_desc = descriptor_at(kv_desc, (j % DqRing) * 2 * DqStepBytes + DqStepBytes);
 #pragma unroll
                 for (int ks = 0; ks < HeadSize / 16; ++ks)
-                    tcgen05_mma_bf16(t + 32, descriptor_at(do_desc, ks * 32), descriptor_at(v_desc, ks * 32), idesc_s,
+                    tcgen05_mma_bf16(tmem_dp, descriptor_at(do_desc, ks * 32), descriptor_at(v_desc, ks * 32), idesc_s,
                                      ks > 0);
-                tcgen05_commit(s_full0 + 8 * stage_in);
-                ++issued;
-                stage_in = stage_in + 1 == DqStages ? 0 : stage_in + 1;
+                tcgen05_commit(dp_full);
             };
             if (ok)
-                issue_scores();
+                issue_s(0);
+            if (ok)
+                issue_dp(0);
             if (ok && blocks > 1)
-                issue_scores();
-            int stage = 0, phase = 0;
+                issue_s(1);
             for (int j = 0; j < blocks && ok; ++j) {
-                ok = mbarrier_wait(ds_full0 + 8 * stage, phase, abort_flag, p.counters, 304);
+                ok = mbarrier_wait(ds_full0 + 8 * (j & 1), (j >> 1) & 1, abort_flag, p.counters, 304);
                 if (!ok)
                     break;
                 tcgen05_fence_after();
-                const int ring = j % Ring;
-                const uint64_t k_desc = descriptor_at(k_mn_desc, ring * 2 * StepBytes);
+                const int ring = j % DqRing;
+                const uint64_t k_desc = descriptor_at(k_mn_desc, ring * 2 * DqStepBytes);
 #pragma unroll
-                for (int ks = 0; ks < Step / 16; ++ks) // dQ += dS K_j: 16 keys (8 packed columns at 16 ks) at a time
-                    tcgen05_mma_bf16_ts(tmem_dq, tmem_base + 64 * stage + ks * 16, descriptor_at(k_desc, ks * 2048),
-                                        idesc_dq, (j > 0 || ks > 0) ? 1u : 0u);
+                for (int ks = 0; ks < DqStep / 16; ++ks) // dQ += dS K_j: 16 keys = 8 packed columns at (ks / 2) 32 + (ks % 2) 8
+                    tcgen05_mma_bf16_ts(tmem_dq, tmem_base + 64 * (j & 1) + (ks / 2) * 32 + (ks % 2) * 8,
+                                        descriptor_at(k_desc, ks * 2048), idesc_dq, (j > 0 || ks > 0) ? 1u : 0u);
                 tcgen05_commit(kv_empty0 + 8 * ring);
-                if (issued < blocks)
-                    issue_scores(); // reuses the stage whose dS the MMAs issued one step ago have read
-                if (++stage == DqStages)
-                    stage = 0, phase ^= 1;
+                if (j + 1 < blocks)
+                    issue_dp(j + 1); // every compute warp has finished with dP of step j
+                if (j + 2 < blocks)
+                    issue_s(j + 2); // into the buffer whose dS the products above have just read
             }
             if (ok)
                 tcgen05_commit(dq_done);
         }
     } else {
-        // Two warps share each 32-lane quarter: warp `half` takes 16 of the step's 32 keys and leaves
-        // its 8 packed dS columns at the start of its own 16 score columns (the other warp may still
-        // be reading its own).
+        // Two warps share each 32-lane quarter; warp `half` takes 32 of the step's 64 keys.
         const int quarter = warp % 4, half = (warp - 2) / 4;
         const int row = quarter * 32 + lane, position = tile * BlockM + row;
         const int warp_first = tile * BlockM + quarter * 32; // earliest query of this warp
@@ -546,50 +553,54 @@ flash_dq_kernel(const __grid_constant__ CUtensorMap map_qkv128, const __grid_con
                     p.delta[stat] = delta;
             }
         }
-        int stage = 0, phase = 0;
         for (int j = 0; j < blocks && ok; ++j) {
-            ok = mbarrier_wait(s_full0 + 8 * stage, phase, abort_flag, p.counters, 305);
+            ok = mbarrier_wait(s_full0 + 8 * (j & 1), (j >> 1) & 1, abort_flag, p.counters, 305);
             if (!ok)
                 break;
             tcgen05_fence_after();
-            uint32_t sc[16], dp[16], packed[8];
-            const uint32_t t = lane_base + 64 * stage;
-            tmem_load_32x16_async(t + half * 16, sc);
-            tmem_load_32x16_async(t + 32 + half * 16, dp);
-            tmem_wait_load(sc);
-            tmem_wait_load(dp);
-            const int key0 = j * Step + half * 16;
-            if (key0 + 15 > warp_first || ragged) { // the causal diagonal crosses this warp's block
+            const uint32_t t = lane_base + 64 * (j & 1) + half * 32; // this warp's 32 score columns
+            const int key0 = j * DqStep + half * 32;
+            const bool none = key0 > warp_first + 31;                  // every key lies after every query of the warp
+            const bool masked = key0 + 31 > warp_first || ragged;      // the causal diagonal crosses the warp's block
+            uint32_t prob[32]; // scores, then probabilities, as FP32 bits
+            if (!none) {
+                tmem_load_32x32_async(t, prob);
+                tmem_wait_load(prob);
 #pragma unroll
-                for (int i = 0; i < 16; i += 2) {
-                    float v[2];
-#pragma unroll
-                    for (int u = 0; u < 2; ++u) {
-                        float prob = fast_exp2(fmaf(__uint_as_float(sc[i + u]), p.scale_log2, -lse2));
-                        float ds = prob * (__uint_as_float(dp[i + u]) - delta);
-                        v[u] = key0 + i + u > position || !valid ? 0.f : ds;
-                    }
-                    packed[i / 2] = pack_bf16(v[0], v[1]);
-                }
-            } else {
-#pragma unroll
-                for (int i = 0; i < 16; i += 2) {
-                    float v[2];
-#pragma unroll
-                    for (int u = 0; u < 2; ++u)
-                        v[u] = fast_exp2(fmaf(__uint_as_float(sc[i + u]), p.scale_log2, -lse2)) *
-                               (__uint_as_float(dp[i + u]) - delta);
-                    packed[i / 2] = pack_bf16(v[0], v[1]);
+                for (int i = 0; i < 32; ++i) {
+                    float v = fast_exp2(fmaf(__uint_as_float(prob[i]), p.scale_log2, -lse2));
+                    if (masked && (key0 + i > position || !valid))
+                        v = 0.f;
+                    prob[i] = __float_as_uint(v);
                 }
             }
-            tmem_store_32x8(t + half * 16, packed);
+            ok = mbarrier_wait(dp_full, j & 1, abort_flag, p.counters, 309);
+            if (!ok)
+                break;
+            tcgen05_fence_after();
+#pragma unroll
+            for (int c = 0; c < 2; ++c) { // 16 keys at a time
+                uint32_t packed[8];
+                if (none) {
+#pragma unroll
+                    for (int i = 0; i < 8; ++i)
+                        packed[i] = 0u;
+                } else {
+                    uint32_t dp[16];
+                    tmem_load_32x16_async(tmem_dp + (uint32_t(quarter * 32) << 16) + half * 32 + c * 16, dp);
+                    tmem_wait_load(dp);
+#pragma unroll
+                    for (int i = 0; i < 16; i += 2)
+                        packed[i / 2] = pack_bf16(__uint_as_float(prob[c * 16 + i]) * (__uint_as_float(dp[i]) - delta),
+                                                  __uint_as_float(prob[c * 16 + i + 1]) * (__uint_as_float(dp[i + 1]) - delta));
+                }
+                tmem_store_32x8(t + c * 8, packed); // over this warp's own, already read, score columns
+            }
             tmem_wait_store();
             tcgen05_fence_before();
             __syncwarp();
             if (lane == 0)
-                mbarrier_arrive(ds_full0 + 8 * stage);
-            if (++stage == DqStages)
-                stage = 0, phase ^= 1;
+                mbarrier_arrive(ds_full0 + 8 * (j & 1));
         }
         if (ok)
             ok = mbarrier_wait(dq_done, 0, abort_flag, p.counters, 306);
@@ -885,7 +896,8 @@ void launch_flash_attention_backward(const void *qkv, const void *out, const voi
     CUtensorMap do128 = make_map_bf16(dout, width, rows, 1, width, 0, HeadSize, 128);
     CUtensorMap do32 = make_map_bf16(dout, width, rows, 1, width, 0, HeadSize, Step);
     const int grid = batch * heads * p.tiles;
-    flash_dq_kernel<<<grid, BackwardThreads, DqShared, s>>>(qkv128, qkv32, do128, p); // also writes delta
+    CUtensorMap qkv64 = make_map_bf16(qkv, uint64_t(3) * width, rows, 1, uint64_t(3) * width, 0, HeadSize, DqStep);
+    flash_dq_kernel<<<grid, BackwardThreads, DqShared, s>>>(qkv128, qkv64, do128, p); // also writes delta
     flash_dkv_kernel<<<grid, BackwardThreads, DkvShared, s>>>(qkv128, qkv32, do32, p);
     CHECK_CUDA(cudaGetLastError());
 }
