@@ -357,11 +357,6 @@ flash_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
 // under 100 KB of shared memory per CTA: two CTAs share an SM.
 // ------------------------------------------------------------------------------------------
 constexpr int BackwardThreads = 320, BackwardTmemColumns = 256; // warp 0 TMA, warp 1 MMA, 8 compute warps
-constexpr int Step = 32;                                        // keys (dq) or queries (dk/dv) per pipeline step
-constexpr int StepBytes = Step * HeadSize * 2;                  // 4 KB: one K, V, Q or dO block
-constexpr int Ring = 4;                                         // shared-memory ring of operand blocks
-constexpr int DkvStages = 2;                                    // score buffers in tensor memory (dk/dv kernel)
-constexpr int DkvShared = 2 * TileBytes + Ring * 2 * StepBytes + Ring * 64 * 4 + 1024 + 256; // + statistics
 
 struct BackwardParams {
     const bf16 *out; // forward output, for delta = rowsum(dO * O)
@@ -619,19 +614,27 @@ flash_dq_kernel(const __grid_constant__ CUtensorMap map_qkv128, const __grid_con
         tmem_dealloc(tmem_base, BackwardTmemColumns);
 }
 
+// dk/dv kernel.  64 queries per step, everything transposed (thread = key row).  One buffer each for
+// S^T = K Q^T and dP^T = V dO^T: the MMA thread issues, per step, dV += P^T dO (frees the score
+// buffer), the next S^T, dK += dS^T Q (frees the dP buffer) and the next dP^T, so the next step's
+// exponentials start after eight MMAs and its dP^T is ready when they end.  Sixteen MMAs per 64
+// queries instead of 24 with 32-wide steps.
+constexpr int DkvStep = 64, DkvStepBytes = DkvStep * HeadSize * 2, DkvRing = 4;
+constexpr int DkvShared = 2 * TileBytes + DkvRing * 2 * DkvStepBytes + DkvRing * 128 * 4 + 1024 + 256; // K, V, ring of (Q, dO), statistics
+
 __global__ void __launch_bounds__(BackwardThreads, 2)
-flash_dkv_kernel(const __grid_constant__ CUtensorMap map_qkv128, const __grid_constant__ CUtensorMap map_qkv32,
-                 const __grid_constant__ CUtensorMap map_do32, BackwardParams p) {
+flash_dkv_kernel(const __grid_constant__ CUtensorMap map_qkv128, const __grid_constant__ CUtensorMap map_qkv64,
+                 const __grid_constant__ CUtensorMap map_do64, BackwardParams p) {
     extern __shared__ uint8_t raw_shared[];
     const uint32_t base = (smem_address(raw_shared) + 1023u) & ~1023u;
     uint8_t *aligned = raw_shared + (base - smem_address(raw_shared));
-    // per ring slot: lse (in base 2) of the step's 32 queries, then their delta
-    float *statistics = reinterpret_cast<float *>(aligned + 2 * TileBytes + Ring * 2 * StepBytes);
-    uint64_t *barriers = reinterpret_cast<uint64_t *>(aligned + 2 * TileBytes + Ring * 2 * StepBytes + Ring * 64 * 4);
-    const uint32_t kv_full = smem_address(barriers), qdo_full0 = kv_full + 8, qdo_empty0 = qdo_full0 + 8 * Ring,
-                   s_full0 = qdo_empty0 + 8 * Ring, pd_full0 = s_full0 + 8 * DkvStages,
-                   acc_done = pd_full0 + 8 * DkvStages; // 2 + 2 Ring + 2 DkvStages = 14 barriers
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(barriers + 2 + 2 * Ring + 2 * DkvStages);
+    // per ring slot: lse (in base 2) of the step's 64 queries, then their delta
+    float *statistics = reinterpret_cast<float *>(aligned + 2 * TileBytes + DkvRing * 2 * DkvStepBytes);
+    uint64_t *barriers = reinterpret_cast<uint64_t *>(aligned + 2 * TileBytes + DkvRing * 2 * DkvStepBytes + DkvRing * 128 * 4);
+    const uint32_t kv_full = smem_address(barriers), qdo_full0 = kv_full + 8, qdo_empty0 = qdo_full0 + 8 * DkvRing,
+                   s_full = qdo_empty0 + 8 * DkvRing, dp_full = s_full + 8, p_full = dp_full + 8, ds_full = p_full + 8,
+                   acc_done = ds_full + 8; // 6 + 2 DkvRing = 14 barriers
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(barriers + 6 + 2 * DkvRing);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
     const uint32_t smem_k = base, smem_v = base + TileBytes, smem_qdo = base + 2 * TileBytes;
 
@@ -640,19 +643,19 @@ flash_dkv_kernel(const __grid_constant__ CUtensorMap map_qkv128, const __grid_co
     const int tile = int(blockIdx.x / pairs); // key tile; early tiles have the most query blocks
     const int bh = blockIdx.x % pairs, b = bh / p.heads, h = bh % p.heads;
     const int row0 = b * p.context;
-    const int first_block = tile * (BlockN / Step), query_blocks = (p.context + Step - 1) / Step;
+    const int first_block = tile * (BlockN / DkvStep), query_blocks = (p.context + DkvStep - 1) / DkvStep;
     const int blocks = query_blocks - first_block; // query blocks first_block .. query_blocks-1
 
     if (threadIdx.x == 0) {
         mbarrier_init(kv_full, 1);
-        for (int s = 0; s < Ring; ++s) {
+        for (int s = 0; s < DkvRing; ++s) {
             mbarrier_init(qdo_full0 + 8 * s, 1);
             mbarrier_init(qdo_empty0 + 8 * s, 1);
         }
-        for (int s = 0; s < DkvStages; ++s) {
-            mbarrier_init(s_full0 + 8 * s, 1);
-            mbarrier_init(pd_full0 + 8 * s, 8);
-        }
+        mbarrier_init(s_full, 1);
+        mbarrier_init(dp_full, 1);
+        mbarrier_init(p_full, 8);
+        mbarrier_init(ds_full, 8);
         mbarrier_init(acc_done, 1);
         *abort_flag = 0;
         fence_barrier_init();
@@ -665,13 +668,13 @@ flash_dkv_kernel(const __grid_constant__ CUtensorMap map_qkv128, const __grid_co
     __syncthreads();
     tcgen05_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    // stage s: S^T at 64 s (P^T packs into columns 0-7 and 16-23 of it), dP^T at 64 s + 32 (dS^T packs
-    // likewise); dV at 128, dK at 192
-    const uint32_t tmem_dv = tmem_base + 64 * DkvStages, tmem_dk = tmem_dv + HeadSize;
+    // S^T at 0 (a half's packed P^T goes to the first 16 columns of its own 32), dP^T at 64 (dS^T likewise);
+    // dV at 128, dK at 192
+    const uint32_t tmem_dp = tmem_base + 64, tmem_dv = tmem_base + 128, tmem_dk = tmem_base + 192;
 
     if (warp == 0) {
-        // The whole warp runs the producer loop: lane 0 issues the TMA loads, every lane fetches one
-        // query's statistics into the ring slot before lane 0's arrival releases them.
+        // The whole warp runs the producer loop: lane 0 issues the TMA loads, every lane fetches two
+        // queries' statistics into the ring slot before lane 0's arrival releases them.
         if (lane == 0) {
             mbarrier_expect_tx(kv_full, 2 * TileBytes);
             tma_load_3d(smem_k, &map_qkv128, p.width + h * HeadSize, row0 + tile * BlockN, 0, kv_full);
@@ -680,156 +683,178 @@ flash_dkv_kernel(const __grid_constant__ CUtensorMap map_qkv128, const __grid_co
         const float *lse = p.lse + (int64_t(b) * p.heads + h) * p.context;
         const float *delta = p.delta + (int64_t(b) * p.heads + h) * p.context;
         for (int i = 0; i < blocks; ++i) {
-            const int ring = i % Ring, q = (first_block + i) * Step + lane;
-            float lse2 = 0.f, dl = 0.f;
-            if (q < p.context) {
-                lse2 = lse[q] * 1.4426950408889634f;
-                dl = delta[q];
-            }
-            bool ok = mbarrier_wait(qdo_empty0 + 8 * ring, ((i / Ring) & 1) ^ 1, abort_flag, p.counters, 311);
+            const int ring = i % DkvRing, q0 = (first_block + i) * DkvStep;
+            float values[4] = {0.f, 0.f, 0.f, 0.f}; // lse2 and delta of queries q0 + lane and q0 + 32 + lane
+#pragma unroll
+            for (int u = 0; u < 2; ++u)
+                if (q0 + u * 32 + lane < p.context) {
+                    values[u] = lse[q0 + u * 32 + lane] * 1.4426950408889634f;
+                    values[2 + u] = delta[q0 + u * 32 + lane];
+                }
+            bool ok = mbarrier_wait(qdo_empty0 + 8 * ring, ((i / DkvRing) & 1) ^ 1, abort_flag, p.counters, 311);
             if (!__all_sync(0xffffffffu, ok))
                 break;
-            statistics[ring * 64 + lane] = lse2;
-            statistics[ring * 64 + 32 + lane] = dl;
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+                statistics[ring * 128 + u * 32 + lane] = values[u];
+                statistics[ring * 128 + 64 + u * 32 + lane] = values[2 + u];
+            }
             __syncwarp();
             if (lane == 0) {
-                const uint32_t bar = qdo_full0 + 8 * ring, dst = smem_qdo + ring * 2 * StepBytes;
-                mbarrier_expect_tx(bar, 2 * StepBytes);
-                tma_load_3d(dst, &map_qkv32, h * HeadSize, row0 + (first_block + i) * Step, 0, bar);
-                tma_load_3d(dst + StepBytes, &map_do32, h * HeadSize, row0 + (first_block + i) * Step, 0, bar);
+                const uint32_t bar = qdo_full0 + 8 * ring, dst = smem_qdo + ring * 2 * DkvStepBytes;
+                mbarrier_expect_tx(bar, 2 * DkvStepBytes);
+                tma_load_3d(dst, &map_qkv64, h * HeadSize, row0 + q0, 0, bar);
+                tma_load_3d(dst + DkvStepBytes, &map_do64, h * HeadSize, row0 + q0, 0, bar);
             }
         }
     } else if (warp == 1) {
         if (elect_one()) {
-            const uint32_t idesc_s = instruction_descriptor(BlockN, Step, 0, 0);
+            const uint32_t idesc_s = instruction_descriptor(BlockN, DkvStep, 0, 0);
             const uint32_t idesc_acc = instruction_descriptor(BlockN, HeadSize, 0, 1);
             // descriptors are built once; every MMA below only offsets them
             const uint64_t k_desc = smem_descriptor(smem_k, 16, 1024), v_desc = smem_descriptor(smem_v, 16, 1024),
                            qdo_desc = smem_descriptor(smem_qdo, 16, 1024),
                            qdo_mn_desc = smem_descriptor(smem_qdo, 8192, 1024);
             bool ok = mbarrier_wait(kv_full, 0, abort_flag, p.counters, 312);
-            int issued = 0;
-            auto issue_scores = [&]() {
-                const int ring = issued % Ring;
-                ok = mbarrier_wait(qdo_full0 + 8 * ring, (issued / Ring) & 1, abort_flag, p.counters, 313);
+            auto issue_s = [&](int i) { // S^T = K Q_i^T; the first use of ring slot i
+                const int ring = i % DkvRing;
+                ok = mbarrier_wait(qdo_full0 + 8 * ring, (i / DkvRing) & 1, abort_flag, p.counters, 313);
                 if (!ok)
                     return;
                 tcgen05_fence_after();
-                const uint32_t t = tmem_base + 64 * (issued % DkvStages);
-                const uint64_t q_desc = descriptor_at(qdo_desc, ring * 2 * StepBytes),
-                               do_desc = descriptor_at(q_desc, StepBytes);
+                const uint64_t q_desc = descriptor_at(qdo_desc, ring * 2 * DkvStepBytes);
 #pragma unroll
-                for (int ks = 0; ks < HeadSize / 16; ++ks) // S^T = K Q_i^T
-                    tcgen05_mma_bf16(t, descriptor_at(k_desc, ks * 32), descriptor_at(q_desc, ks * 32), idesc_s, ks > 0);
-#pragma unroll
-                for (int ks = 0; ks < HeadSize / 16; ++ks) // dP^T = V dO_i^T
-                    tcgen05_mma_bf16(t + 32, descriptor_at(v_desc, ks * 32), descriptor_at(do_desc, ks * 32), idesc_s,
+                for (int ks = 0; ks < HeadSize / 16; ++ks)
+                    tcgen05_mma_bf16(tmem_base, descriptor_at(k_desc, ks * 32), descriptor_at(q_desc, ks * 32), idesc_s,
                                      ks > 0);
-                tcgen05_commit(s_full0 + 8 * (issued % DkvStages));
-                ++issued;
+                tcgen05_commit(s_full);
+            };
+            auto issue_dp = [&](int i) { // dP^T = V dO_i^T (the slot was awaited by issue_s(i))
+                const uint64_t do_desc = descriptor_at(qdo_desc, (i % DkvRing) * 2 * DkvStepBytes + DkvStepBytes);
+#pragma unroll
+                for (int ks = 0; ks < HeadSize / 16; ++ks)
+                    tcgen05_mma_bf16(tmem_dp, descriptor_at(v_desc, ks * 32), descriptor_at(do_desc, ks * 32), idesc_s,
+                                     ks > 0);
+                tcgen05_commit(dp_full);
             };
             if (ok)
-                issue_scores();
-            if (ok && blocks > 1)
-                issue_scores();
+                issue_s(0);
+            if (ok)
+                issue_dp(0);
             for (int i = 0; i < blocks && ok; ++i) {
-                const int stage = i % DkvStages, ring = i % Ring;
-                ok = mbarrier_wait(pd_full0 + 8 * stage, (i / DkvStages) & 1, abort_flag, p.counters, 314);
+                const int ring = i % DkvRing;
+                const uint64_t q_mn = descriptor_at(qdo_mn_desc, ring * 2 * DkvStepBytes),
+                               do_mn = descriptor_at(q_mn, DkvStepBytes);
+                ok = mbarrier_wait(p_full, i & 1, abort_flag, p.counters, 314);
                 if (!ok)
                     break;
                 tcgen05_fence_after();
-                const uint64_t q_desc = descriptor_at(qdo_mn_desc, ring * 2 * StepBytes),
-                               do_desc = descriptor_at(q_desc, StepBytes);
-                const uint32_t t = tmem_base + 64 * stage;
 #pragma unroll
-                for (int ks = 0; ks < Step / 16; ++ks) // dV += P^T dO_i
-                    tcgen05_mma_bf16_ts(tmem_dv, t + ks * 16, descriptor_at(do_desc, ks * 2048), idesc_acc,
-                                        (i > 0 || ks > 0) ? 1u : 0u);
+                for (int ks = 0; ks < DkvStep / 16; ++ks) // dV += P^T dO_i: 16 queries = 8 packed columns at (ks / 2) 32 + (ks % 2) 8
+                    tcgen05_mma_bf16_ts(tmem_dv, tmem_base + (ks / 2) * 32 + (ks % 2) * 8, descriptor_at(do_mn, ks * 2048),
+                                        idesc_acc, (i > 0 || ks > 0) ? 1u : 0u);
+                if (i + 1 < blocks)
+                    issue_s(i + 1); // into the buffer whose P^T the products above have just read
+                if (!ok)
+                    break;
+                ok = mbarrier_wait(ds_full, i & 1, abort_flag, p.counters, 320);
+                if (!ok)
+                    break;
+                tcgen05_fence_after();
 #pragma unroll
-                for (int ks = 0; ks < Step / 16; ++ks) // dK += dS^T Q_i
-                    tcgen05_mma_bf16_ts(tmem_dk, t + 32 + ks * 16, descriptor_at(q_desc, ks * 2048), idesc_acc,
-                                        (i > 0 || ks > 0) ? 1u : 0u);
+                for (int ks = 0; ks < DkvStep / 16; ++ks) // dK += dS^T Q_i
+                    tcgen05_mma_bf16_ts(tmem_dk, tmem_dp + (ks / 2) * 32 + (ks % 2) * 8, descriptor_at(q_mn, ks * 2048),
+                                        idesc_acc, (i > 0 || ks > 0) ? 1u : 0u);
                 tcgen05_commit(qdo_empty0 + 8 * ring);
-                if (issued < blocks)
-                    issue_scores(); // into the stage the products above have just read
+                if (i + 1 < blocks)
+                    issue_dp(i + 1); // after the products that read dS^T from the same columns
             }
             if (ok)
                 tcgen05_commit(acc_done);
         }
     } else {
-        // Two warps share each 32-lane quarter and take 16 of the step's 32 queries each; their packed
-        // P^T / dS^T columns sit at the start of their own 16 columns.
+        // Two warps share each 32-lane quarter; warp `half` takes 32 of the step's 64 queries.
         const int quarter = warp % 4, half = (warp - 2) / 4;
         const int row = quarter * 32 + lane, key = tile * BlockN + row; // key position inside the sequence
-        const int warp_last = tile * BlockN + quarter * 32 + 31;        // latest key of this warp
-        const uint32_t lane_base = tmem_base + (uint32_t(quarter * 32) << 16);
+        const int warp_first = tile * BlockN + quarter * 32;            // earliest key of this warp
+        const uint32_t lanes = uint32_t(quarter * 32) << 16;
+        const uint32_t t_s = tmem_base + lanes + half * 32, t_dp = tmem_dp + lanes + half * 32; // this warp's 32 columns
         bool ok = true;
         for (int i = 0; i < blocks; ++i) {
-            const int stage = i % DkvStages, ring = i % Ring;
-            ok = mbarrier_wait(qdo_full0 + 8 * ring, (i / Ring) & 1, abort_flag, p.counters, 317) && // statistics
-                 mbarrier_wait(s_full0 + 8 * stage, (i / DkvStages) & 1, abort_flag, p.counters, 315);
+            const int ring = i % DkvRing;
+            ok = mbarrier_wait(qdo_full0 + 8 * ring, (i / DkvRing) & 1, abort_flag, p.counters, 317) && // statistics
+                 mbarrier_wait(s_full, i & 1, abort_flag, p.counters, 315);
             if (!ok)
                 break;
             tcgen05_fence_after();
-            uint32_t sc[16], dp[16], pp[8], pd[8];
-            const uint32_t t = lane_base + 64 * stage + half * 16;
-            tmem_load_32x16_async(t, sc);
-            tmem_load_32x16_async(t + 32, dp);
-            float l2[16], dl[16];
-            const float4 *stats = reinterpret_cast<const float4 *>(statistics + ring * 64 + half * 16);
+            const float *l2 = statistics + ring * 128 + half * 32, *dl = l2 + 64;
+            const int qa = (first_block + i) * DkvStep + half * 32;         // first query of this warp's columns
+            const bool none = qa + 31 < warp_first;                         // every query lies before every key of the warp
+            const bool masked = qa < warp_first + 31 || qa + 32 > p.context; // causal diagonal or ragged end
+            uint32_t prob[32]; // scores, then probabilities, as FP32 bits
+            {
+                uint32_t pp[16];
+                if (none) {
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                const float4 a = stats[c], d = stats[8 + c];
-                l2[4 * c] = a.x, l2[4 * c + 1] = a.y, l2[4 * c + 2] = a.z, l2[4 * c + 3] = a.w;
-                dl[4 * c] = d.x, dl[4 * c + 1] = d.y, dl[4 * c + 2] = d.z, dl[4 * c + 3] = d.w;
-            }
-            tmem_wait_load(sc);
-            tmem_wait_load(dp);
-            const int qa = (first_block + i) * Step + half * 16; // first query of this warp's columns
-            if (qa < warp_last || qa + 16 > p.context) {         // causal diagonal or ragged end
+                    for (int c = 0; c < 16; ++c)
+                        pp[c] = 0u;
+                } else {
+                    tmem_load_32x32_async(t_s, prob);
+                    tmem_wait_load(prob);
 #pragma unroll
-                for (int c = 0; c < 16; c += 2) {
-                    float pv[2], dv[2];
-#pragma unroll
-                    for (int u = 0; u < 2; ++u) {
-                        float prob = fast_exp2(fmaf(__uint_as_float(sc[c + u]), p.scale_log2, -l2[c + u]));
-                        if (qa + c + u < key || qa + c + u >= p.context)
-                            prob = 0.f;
-                        pv[u] = prob;
-                        dv[u] = prob * (__uint_as_float(dp[c + u]) - dl[c + u]);
+                    for (int c = 0; c < 32; ++c) {
+                        float v = fast_exp2(fmaf(__uint_as_float(prob[c]), p.scale_log2, -l2[c]));
+                        if (masked && (qa + c < key || qa + c >= p.context))
+                            v = 0.f;
+                        prob[c] = __float_as_uint(v);
                     }
-                    pp[c / 2] = pack_bf16(pv[0], pv[1]);
-                    pd[c / 2] = pack_bf16(dv[0], dv[1]);
-                }
-            } else {
 #pragma unroll
-                for (int c = 0; c < 16; c += 2) {
-                    float pv[2], dv[2];
-#pragma unroll
-                    for (int u = 0; u < 2; ++u) {
-                        pv[u] = fast_exp2(fmaf(__uint_as_float(sc[c + u]), p.scale_log2, -l2[c + u]));
-                        dv[u] = pv[u] * (__uint_as_float(dp[c + u]) - dl[c + u]);
-                    }
-                    pp[c / 2] = pack_bf16(pv[0], pv[1]);
-                    pd[c / 2] = pack_bf16(dv[0], dv[1]);
+                    for (int c = 0; c < 32; c += 2)
+                        pp[c / 2] = pack_bf16(__uint_as_float(prob[c]), __uint_as_float(prob[c + 1]));
                 }
+                tmem_store_32x16(t_s, pp); // over this warp's own, already read, score columns
+                tmem_wait_store();
+                tcgen05_fence_before();
+                __syncwarp();
+                if (lane == 0)
+                    mbarrier_arrive(p_full);
             }
-            tmem_store_32x8(t, pp);
-            tmem_store_32x8(t + 32, pd);
+            ok = mbarrier_wait(dp_full, i & 1, abort_flag, p.counters, 319);
+            if (!ok)
+                break;
+            tcgen05_fence_after();
+#pragma unroll
+            for (int c = 0; c < 2; ++c) { // 16 queries at a time
+                uint32_t pd[8];
+                if (none) {
+#pragma unroll
+                    for (int e = 0; e < 8; ++e)
+                        pd[e] = 0u;
+                } else {
+                    uint32_t dp[16];
+                    tmem_load_32x16_async(t_dp + c * 16, dp);
+                    tmem_wait_load(dp);
+#pragma unroll
+                    for (int e = 0; e < 16; e += 2)
+                        pd[e / 2] = pack_bf16(
+                            __uint_as_float(prob[c * 16 + e]) * (__uint_as_float(dp[e]) - dl[c * 16 + e]),
+                            __uint_as_float(prob[c * 16 + e + 1]) * (__uint_as_float(dp[e + 1]) - dl[c * 16 + e + 1]));
+                }
+                tmem_store_32x8(t_dp + c * 8, pd); // over this warp's own, already read, columns
+            }
             tmem_wait_store();
             tcgen05_fence_before();
             __syncwarp();
             if (lane == 0)
-                mbarrier_arrive(pd_full0 + 8 * stage);
+                mbarrier_arrive(ds_full);
         }
         if (ok)
             ok = mbarrier_wait(acc_done, 0, abort_flag, p.counters, 316);
         if (ok) {
             tcgen05_fence_after();
             bf16 *out = p.dqkv + (int64_t(row0) + key) * 3 * p.width + h * HeadSize + half * 32;
-            const uint32_t lanes = (uint32_t(quarter * 32) << 16) + half * 32;
-            store_accumulator(tmem_dk + lanes, out + p.width, p.scale, key < p.context);
-            store_accumulator(tmem_dv + lanes, out + 2 * p.width, 1.f, key < p.context);
+            store_accumulator(tmem_dk + lanes + half * 32, out + p.width, p.scale, key < p.context);
+            store_accumulator(tmem_dv + lanes + half * 32, out + 2 * p.width, 1.f, key < p.context);
         }
     }
     __syncthreads();
@@ -892,12 +917,12 @@ void launch_flash_attention_backward(const void *qkv, const void *out, const voi
     p.counters = counters;
     const uint64_t rows = uint64_t(batch) * context;
     CUtensorMap qkv128 = make_map_bf16(qkv, uint64_t(3) * width, rows, 1, uint64_t(3) * width, 0, HeadSize, 128);
-    CUtensorMap qkv32 = make_map_bf16(qkv, uint64_t(3) * width, rows, 1, uint64_t(3) * width, 0, HeadSize, Step);
+
     CUtensorMap do128 = make_map_bf16(dout, width, rows, 1, width, 0, HeadSize, 128);
-    CUtensorMap do32 = make_map_bf16(dout, width, rows, 1, width, 0, HeadSize, Step);
+    CUtensorMap do64 = make_map_bf16(dout, width, rows, 1, width, 0, HeadSize, DkvStep);
     const int grid = batch * heads * p.tiles;
     CUtensorMap qkv64 = make_map_bf16(qkv, uint64_t(3) * width, rows, 1, uint64_t(3) * width, 0, HeadSize, DqStep);
     flash_dq_kernel<<<grid, BackwardThreads, DqShared, s>>>(qkv128, qkv64, do128, p); // also writes delta
-    flash_dkv_kernel<<<grid, BackwardThreads, DkvShared, s>>>(qkv128, qkv32, do32, p);
+    flash_dkv_kernel<<<grid, BackwardThreads, DkvShared, s>>>(qkv128, qkv64, do64, p);
     CHECK_CUDA(cudaGetLastError());
 }
