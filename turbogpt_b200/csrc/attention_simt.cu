@@ -296,44 +296,6 @@ template <class T> __global__ void __launch_bounds__(AttentionWarps * 32) attent
             out[2 * a.width + j * 32 + lane] = from_float<T>(dv[j]);
         }
 }
-// Head size 64: eight lanes cover one (token, head) with one 128-bit load each from dout and out.
-template <class T> __global__ void __launch_bounds__(256) attention_delta64_kernel(SoftmaxAttentionBackwardArgs a) {
-    const int groups_per_row = a.width / 8;
-    const int64_t group = blockIdx.x * int64_t(blockDim.x) + threadIdx.x;
-    const int64_t rows = int64_t(a.batch) * a.context;
-    const bool active = group < rows * groups_per_row;
-    float sum = 0;
-    int64_t row = 0;
-    int head = 0;
-    if (active) {
-        row = group / groups_per_row;
-        const int c = int(group % groups_per_row) * 8;
-        head = c / 64;
-        float x[8], y[8];
-        load8((const T *)a.dout + row * a.width + c, x);
-        load8((const T *)a.out + row * a.width + c, y);
-#pragma unroll
-        for (int j = 0; j < 8; ++j)
-            sum += x[j] * y[j];
-    }
-#pragma unroll
-    for (int k = 4; k; k >>= 1)
-        sum += __shfl_xor_sync(0xffffffffu, sum, k);
-    if (active && threadIdx.x % 8 == 0) {
-        const int64_t b = row / a.context, t = row % a.context;
-        a.delta[(b * a.heads + head) * a.context + t] = sum;
-    }
-}
-void launch_attention_delta(Dtype t, const SoftmaxAttentionBackwardArgs &a, cudaStream_t s) {
-    int64_t items = int64_t(a.batch) * a.heads * a.context;
-    if (a.width == a.heads * 64) {
-        int64_t groups = int64_t(a.batch) * a.context * (a.width / 8);
-        DISPATCH(t, (attention_delta64_kernel<T><<<int((groups + 255) / 256), 256, 0, s>>>(a)));
-        return;
-    }
-    DISPATCH(t, (attention_delta_kernel<T><<<int((items + AttentionWarps - 1) / AttentionWarps), AttentionWarps * 32,
-                                            0, s>>>(a)));
-}
 void launch_softmax_attention_backward(Dtype t, const SoftmaxAttentionBackwardArgs &a, cudaStream_t s) {
     int64_t items = int64_t(a.batch) * a.heads * a.context;
     int d = a.width / a.heads;

@@ -105,8 +105,6 @@ bool flash_attention_supported(int width, int heads);
 void launch_flash_attention_forward(const void *qkv, void *out, float *lse, int batch, int context, int heads,
                                     StepCounters *counters, cudaStream_t s);
 
-// delta = rowsum(dout * out) into a.delta; lse/dqkv of `a` are not touched.
-void launch_attention_delta(Dtype t, const SoftmaxAttentionBackwardArgs &a, cudaStream_t s);
 // `delta` ([batch, heads, context] floats) is scratch: the dq kernel fills it with rowsum(dout * out).
 void launch_flash_attention_backward(const void *qkv, const void *out, const void *dout, const float *lse,
                                      float *delta, void *dqkv, int batch, int context, int heads,
