@@ -83,7 +83,8 @@ def test_cross_entropy_matches_torch():
 
 
 @pytest.mark.parametrize("batch,context,heads,d_head", [(2, 128, 2, 64), (1, 200, 3, 64), (2, 64, 2, 32),
-                                                        (2, 1024, 2, 64), (3, 520, 1, 64)])
+                                                        (2, 1024, 2, 64), (3, 520, 1, 64), (1, 8, 1, 64),
+                                                        (2, 40, 2, 64), (1, 65, 1, 64)])
 def test_attention_matches_torch(batch, context, heads, d_head):
     lib = load_library()
     width = heads * d_head
