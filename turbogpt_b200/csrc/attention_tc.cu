@@ -64,6 +64,7 @@ flash_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     const int last_key = min(p.context, (tile + 1) * BlockM);
     const int steps = (last_key + KeyStep - 1) / KeyStep; // causal: keys 0 .. last_key - 1, 64 per step
 
+    grid_launch_dependents(); // the next kernel may set itself up while this one runs
     if (threadIdx.x == 0) {
         mbarrier_init(q_full, 1);
         for (int s = 0; s < ForwardRing; ++s) {
@@ -415,6 +416,7 @@ flash_dq_kernel(const __grid_constant__ CUtensorMap map_qkv128, const __grid_con
     const int last_key = min(p.context, (tile + 1) * BlockM); // keys 0..last_key-1 can be attended
     const int blocks = (last_key + DqStep - 1) / DqStep;
 
+    grid_launch_dependents(); // the next kernel may set itself up while this one runs
     if (threadIdx.x == 0) {
         mbarrier_init(qdo_full, 1);
         for (int s = 0; s < DqRing; ++s) {
@@ -646,6 +648,7 @@ flash_dkv_kernel(const __grid_constant__ CUtensorMap map_qkv128, const __grid_co
     const int first_block = tile * (BlockN / DkvStep), query_blocks = (p.context + DkvStep - 1) / DkvStep;
     const int blocks = query_blocks - first_block; // query blocks first_block .. query_blocks-1
 
+    grid_launch_dependents(); // the next kernel may set itself up while this one runs
     if (threadIdx.x == 0) {
         mbarrier_init(kv_full, 1);
         for (int s = 0; s < DkvRing; ++s) {

@@ -4,6 +4,7 @@
 // reductions.
 #include "device_utils.cuh"
 #include "kernels.cuh"
+#include "sm100.cuh"
 
 #define DISPATCH(t, ...)                                                                                    \
     do {                                                                                                    \
@@ -282,6 +283,7 @@ template <int V> __device__ __forceinline__ void row_moments(int kind, const flo
     inv = rsqrtf(warp_sum((centred[0] + centred[1]) + (centred[2] + centred[3])) / width + 1e-5f);
 }
 template <class T, int V> __global__ void __launch_bounds__(256, 4) norm_rows_kernel(NormArgs a) {
+    sm100::grid_launch_dependents(); // the next kernel may set itself up while this one runs
     __shared__ __align__(16) float sw[V * 256], sb[V * 256]; // FP32 scale and bias, shared by the block's rows
     const int lane = threadIdx.x % 32, warps = blockDim.x / 32;
     for (int c = threadIdx.x; c < V * 256; c += blockDim.x) {
@@ -428,6 +430,7 @@ __global__ void __launch_bounds__(256) norm_backward_reduce_kernel(const float *
 // gradient sums of its rows in its own slice of shared memory (a lane owns its columns there);
 // warps are summed in order at the end, blocks in order by the reduce kernel: deterministic.
 template <class T, int V> __global__ void __launch_bounds__(256, 2) norm_backward_rows_kernel(NormBackwardArgs a) {
+    sm100::grid_launch_dependents(); // the next kernel may set itself up while this one runs
     extern __shared__ float sums[]; // [V * 256] scale, then [warps][2][V * 256] gradient sums
     const int lane = threadIdx.x % 32, warp = threadIdx.x / 32, warps = blockDim.x / 32;
     float *scale = sums, *mine = sums + V * 256 + warp * 2 * V * 256;

@@ -203,6 +203,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         cluster_sync_all(); // the partner's barriers exist before anything signals them
     tcgen05_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    // Barriers, tensor memory and descriptors are set up; only now wait for the kernel before this one
+    // (its tail overlaps the set-up above when this kernel was launched programmatically).
+    grid_launch_dependents();
+    grid_dependency_wait();
 
     // Tiles along M are scheduled per CTA pair; m_tiles counts 128-row tiles including padding.
     const int m_tiles = ((p.m + BM * Unit - 1) / (BM * Unit)) * Unit, n_tiles = (p.n + p.bn - 1) / p.bn;
@@ -703,10 +707,13 @@ void launch_gemm_tc(const GemmArgs &g, int sms, StepCounters *counters, cudaStre
         cudaLaunchConfig_t config{};
         config.gridDim = dim3(grid), config.blockDim = dim3(Threads);
         config.dynamicSmemBytes = shared, config.stream = s;
-        cudaLaunchAttribute cluster{};
-        cluster.id = cudaLaunchAttributeClusterDimension;
-        cluster.val.clusterDim.x = unit, cluster.val.clusterDim.y = 1, cluster.val.clusterDim.z = 1;
-        config.attrs = &cluster, config.numAttrs = 1;
+        static const bool programmatic = getenv("TURBOGPT_NO_PDL") == nullptr;
+        cudaLaunchAttribute attributes[2]{};
+        attributes[0].id = cudaLaunchAttributeClusterDimension;
+        attributes[0].val.clusterDim.x = unit, attributes[0].val.clusterDim.y = 1, attributes[0].val.clusterDim.z = 1;
+        attributes[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attributes[1].val.programmaticStreamSerializationAllowed = 1;
+        config.attrs = attributes, config.numAttrs = programmatic ? 2 : 1;
         CHECK_CUDA(cudaLaunchKernelEx(&config, kernel, map_a, map_b, map_c, map_c, map_c, p));
     };
     auto launch_kind = [&](auto pair_tag) {

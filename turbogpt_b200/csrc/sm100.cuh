@@ -5,6 +5,7 @@
 #pragma once
 #include "common.h"
 #include "kernels.cuh"
+#include <cstdlib>
 #include <cuda.h>
 
 namespace sm100 {
@@ -70,6 +71,13 @@ __device__ __forceinline__ unsigned long long global_timer() {
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
     return t;
 }
+
+// Programmatic dependent launch: a kernel launched with the programmatic-serialization attribute may
+// start (and run its prologue) once every CTA of the kernel before it in the stream has called
+// grid_launch_dependents() or exited; grid_dependency_wait() then blocks until that kernel has
+// completed and its writes are visible.  Both are no-ops for kernels launched the ordinary way.
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
 __device__ __forceinline__ void mbarrier_init(uint32_t bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
