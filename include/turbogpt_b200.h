@@ -11,7 +11,10 @@
  * Error convention (runtime.h:39-42): int results are < 0 on failure and pointer
  * results are NULL; tg_error() returns the calling thread's last message.  No C++
  * exception crosses this boundary.  An Engine is not thread-safe; it owns one CUDA
- * stream and every call selects the engine's device first.
+ * stream, every call selects the engine's device first, and all its scratch memory (the GEMM's split-K
+ * workspace included) is its own, so several engines may run on one GPU at once.  The stand-alone
+ * kernel calls of part 2 (tg_ex_gemm, ...) share one per-device workspace: calls that overlap on the
+ * GPU (different streams or threads) race on it.
  */
 #ifndef TURBOGPT_B200_H
 #define TURBOGPT_B200_H
@@ -87,7 +90,10 @@ enum { TG_PRECISION_BF16 = 0, TG_PRECISION_FP32 = 1 };
 enum { TG_FLAG_NO_TENSOR_CORES = 1, /* route every GEMM and attention through the plain CUDA-core kernels */
        TG_FLAG_PROFILE = 2,         /* time every kernel family with CUDA events (serialises nothing, disables graph replay) */
        TG_FLAG_BF16_GRADIENT_EXCHANGE = 4, /* all-reduce gradients as BF16 instead of FP32 */
-       TG_FLAG_NO_GRAPH = 8         /* launch every kernel of tg_train directly instead of replaying a CUDA graph of the step */ };
+       TG_FLAG_NO_GRAPH = 8,        /* launch every kernel of tg_train directly instead of replaying a CUDA graph of the step */
+       TG_FLAG_NO_COMMUNICATOR = 16 /* world > 1 without NCCL: world/rank only shard the sampling (tg_ex_sample) and scale the
+                                       loss by the global batch (tg_batch gradients are this rank's share of the global mean);
+                                       the caller sums gradients itself, tg_train and tg_ex_train_batch are refused */ };
 
 /* Replaces the compile-time "Width=16, heads=4" of config.h:4 and the hard-wired sizes of
  * model.h:20-34.  `base` keeps the reference's meaning.  struct_size must be
@@ -119,6 +125,11 @@ int tg_ex_parameter_layout(const TgConfigEx *config, int64_t *offsets, int32_t *
                            int capacity);
 /* initialize_weights of model.cpp:7-31 for any architecture (same seeds per tensor role). */
 int tg_ex_initialize_weights(const TgConfigEx *config, float *weights);
+/* A digest of everything the ranks of one data-parallel job must agree on (every field of *config
+ * except rank and base.device; nccl_id included).  Ranks exchange it over their own channel and
+ * refuse to call tg_create_ex when the values differ: a communicator created from mismatched
+ * configurations would hang or train garbage.  0 (and tg_error) when *config is invalid. */
+uint64_t tg_ex_config_digest(const TgConfigEx *config);
 /* 128-byte NCCL unique id for TgConfigEx.nccl_id. */
 int tg_ex_nccl_unique_id(uint8_t *id128);
 /* The engine's CUDA stream (cudaStream_t), for callers that time with their own events. */
@@ -138,6 +149,20 @@ int tg_ex_profile(Engine *engine, const char **names, double *milliseconds, int6
                   int capacity, int reset);
 /* Number of kernels this library launched on the engine's stream since creation. */
 int64_t tg_ex_launch_count(Engine *engine);
+/* Diagnostic: copies an activation saved by the last forward pass (tg_batch / tg_train keep them for
+ * backward; the reference keeps the same set in its Activation struct, cuda/types.cuh:40-44) to
+ * host FP32.  layer >= 0: "x", "normed1", "qkv", "attended", "middle", "normed2", "activated";
+ * layer < 0: "final_x", "final_normed".  Returns the element count (tokens x features), also when
+ * out == NULL; < 0 on an unknown name or a short buffer. */
+int64_t tg_ex_read_activation(Engine *engine, int layer, const char *name, float *out, int64_t capacity);
+
+/* Self-test of the bounded device waits (the reference's waits are unbounded, cuda/pipeline.cuh:24-25):
+ * one CTA waits, for at most `limit_ms` (0 < limit_ms <= 100), on a barrier that nothing arms, with no
+ * copy or tensor-core operation in flight.  Returns 1 when the wait gave up as designed and left code
+ * 901 in the engine's device error word (0 if it reported completion, < 0 on a host error).  The
+ * engine's next synchronising call (tg_batch, tg_get_training_losses, tg_predict, tg_optimizer_test)
+ * then fails with "a device-side wait gave up (code 901)"; tg_set_weights clears the error word. */
+int tg_ex_selftest_bounded_wait(Engine *engine, double limit_ms);
 
 /* Kernel microbenchmarks on device pointers (BF16 unless noted), enqueued on `stream`.
  * C[M,N] = A . B^T with element strides: A[m,k] at m*a_row + k*a_col, B[n,k] at n*b_row + k*b_col;
@@ -157,6 +182,12 @@ int tg_ex_gemm(const void *a, int64_t a_row, int64_t a_col, const void *b, int64
  * cleared on `stream` first): calls that overlap on the GPU race.  Results equal tg_ex_gemm's. */
 int tg_ex_weight_gradient_static(const void *dy, const void *x, float *dw, int out, int in, int tokens,
                                  void *stream);
+/* tg_ex_gemm and tg_ex_weight_gradient_static return once their kernel is enqueued.  Every wait inside
+ * the kernel is bounded (about two seconds); one that gives up leaves a code in a device error word
+ * and the output partly unwritten.  This call synchronises `stream` and returns the first such code
+ * recorded on the current device since the last query (0: none; < 0: host error), clearing it.
+ * Allocates nothing. */
+int tg_ex_last_device_error(void *stream);
 /* Causal softmax attention over packed qkv [batch*context, 3*heads*d_head] (q | k | v);
  * out [batch*context, heads*d_head]; lse [batch, heads, context] floats. */
 int tg_ex_attention_forward(const void *qkv, void *out, float *lse, int batch, int context, int heads,

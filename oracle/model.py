@@ -14,6 +14,9 @@ Two architectures share one code path:
   straight-through gradient (tests/reference.py:14-21), norm math in FP32 then BF16
   (tests/reference.py:53-54), BF16 activations between ops, FP32 logits
   (tests/reference.py:81), mean cross-entropy over batch x context (tests/verify.py:26-27).
+  Softmax attention rounds where a fused kernel has to: the unnormalised probabilities
+  exp(s - rowmax) go to BF16 for the product with V (they are a tensor-core operand), their FP32
+  sum divides the result afterwards.
 
 ``fp32=True`` switches every rounding off (weights untruncated, FP32 activations): the
 check mode whose tolerance is 1e-5.
@@ -136,9 +139,15 @@ class Model:
             p.grad = None
 
     # -- forward ---------------------------------------------------------------------
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
-        """x: int64 [B, T] bytes -> FP32 logits [B, T, 256]."""
+    def forward(self, x: torch.Tensor, trace: dict | None = None) -> torch.Tensor:
+        """x: int64 [B, T] bytes -> FP32 logits [B, T, 256].  ``trace``, when given, receives every
+        layer's intermediate activations as FP32 arrays [B*T, features] under "<layer>.<name>"."""
         a, p = self.arch, self.params
+
+        def keep(name, t):
+            if trace is not None:
+                trace[name] = t.detach().float().reshape(-1, t.shape[-1]).numpy()
+
         act = (lambda t: t.float()) if self.fp32 else (lambda t: t.bfloat16())
         if self.fp32:
             q = {n: v for n, v in p.items() if not is_norm(n)}
@@ -167,7 +176,11 @@ class Model:
         mask = torch.ones(T, T, dtype=torch.bool).tril()
         for l in range(a.depth):
             s = f"{l}."
-            packed = linear(norm(h, s + "ln1"), s + "qkv")
+            keep(s + "x", h)
+            n1 = norm(h, s + "ln1")
+            keep(s + "normed1", n1)
+            packed = linear(n1, s + "qkv")
+            keep(s + "qkv", packed)
             query, key, value = [t.reshape(B, T, H, D).transpose(1, 2) for t in packed.split(W, -1)]
             if a.rope == "partial":
                 query, key = rope(query), rope(key)
@@ -177,19 +190,31 @@ class Model:
                 selected = value.gather(2, index.expand(-1, -1, -1, D))
                 out = act(selected.float() * F.gelu(top))
             else:
-                weights = torch.softmax((scores / math.sqrt(D)).masked_fill(~mask, float("-inf")), -1)
-                out = act(weights @ value.float())
-            h = h + linear(out.transpose(1, 2).reshape(B, T, W), s + "attention")
+                scaled = (scores / math.sqrt(D)).masked_fill(~mask, float("-inf"))
+                if self.fp32:
+                    out = torch.softmax(scaled, -1) @ value.float()
+                else:
+                    unnormalised = torch.exp(scaled - scaled.max(-1, keepdim=True).values)
+                    out = act((act(unnormalised).float() @ value.float()) / unnormalised.sum(-1, keepdim=True))
+            out = out.transpose(1, 2).reshape(B, T, W)
+            keep(s + "attended", out)
+            h = h + linear(out, s + "attention")
+            keep(s + "middle", h)
             n2 = norm(h, s + "ln2")
+            keep(s + "normed2", n2)
             if a.mlp == "swiglu":
                 # one packed projection = one BF16 input-gradient rounding (tests/reference.py:77-79)
                 gate, up = F.linear(n2, torch.cat((q[s + "gate"], q[s + "up"]))).split(a.hidden, -1)
                 middle = F.silu(gate) * up
             else:
                 middle = act(F.gelu(linear(n2, s + "gate").float()))
+            keep(s + "activated", middle)
             h = h + linear(middle, s + "projection")
+        keep("final_x", h)
+        final = norm(h, "final")
+        keep("final_normed", final)
         head = q["embedding"] if a.tied else q["head"]
-        return F.linear(norm(h, "final"), head).float()
+        return F.linear(final, head).float()
 
     # -- one evaluation the way tg_batch reports it -------------------------------------
     def batch(self, x: np.ndarray, y: np.ndarray, backward: bool = True, divisor: int | None = None):

@@ -20,7 +20,7 @@ MLP_SWIGLU, MLP_GELU = 0, 1
 ROPE_NONE, ROPE_PARTIAL = 0, 1
 HIDDEN_MUON, HIDDEN_ADAMW = 0, 1
 PRECISION_BF16, PRECISION_FP32 = 0, 1
-FLAG_NO_TENSOR_CORES, FLAG_PROFILE, FLAG_BF16_GRADIENT_EXCHANGE, FLAG_NO_GRAPH = 1, 2, 4, 8
+FLAG_NO_TENSOR_CORES, FLAG_PROFILE, FLAG_BF16_GRADIENT_EXCHANGE, FLAG_NO_GRAPH, FLAG_NO_COMMUNICATOR = 1, 2, 4, 8, 16
 
 
 class Config(C.Structure):
@@ -151,6 +151,8 @@ def load_library() -> C.CDLL:
     lib.tg_ex_parameter_count.restype = I64
     lib.tg_ex_parameter_layout.argtypes = [C.POINTER(ConfigEx), P, P, P, I]
     lib.tg_ex_initialize_weights.argtypes = [C.POINTER(ConfigEx), P]
+    lib.tg_ex_config_digest.argtypes = [C.POINTER(ConfigEx)]
+    lib.tg_ex_config_digest.restype = C.c_uint64
     lib.tg_ex_nccl_unique_id.argtypes = [P]
     lib.tg_ex_stream.argtypes = [P]
     lib.tg_ex_stream.restype = P
@@ -158,10 +160,14 @@ def load_library() -> C.CDLL:
     lib.tg_ex_train_mean_loss.argtypes = [P, I, C.POINTER(C.c_float)]
     lib.tg_ex_train_batch.argtypes = [P, P, P, P]
     lib.tg_ex_profile.argtypes = [P, P, P, P, I, I]
+    lib.tg_ex_selftest_bounded_wait.argtypes = [P, C.c_double]
     lib.tg_ex_launch_count.argtypes = [P]
     lib.tg_ex_launch_count.restype = I64
+    lib.tg_ex_read_activation.argtypes = [P, I, C.c_char_p, P, I64]
+    lib.tg_ex_read_activation.restype = I64
     lib.tg_ex_gemm.argtypes = [P, I64, I64, P, I64, I64, P, I64, I, I, I, I, I, P]
     lib.tg_ex_weight_gradient_static.argtypes = [P, P, P, I, I, I, P]
+    lib.tg_ex_last_device_error.argtypes = [P]
     lib.tg_ex_attention_forward.argtypes = [P, P, P, I, I, I, I, I, P]
     lib.tg_ex_attention_backward.argtypes = [P, P, P, P, P, I, I, I, I, I, P]
     lib.tg_ex_cross_entropy.argtypes = [P, P, P, P, I, C.c_float, P]
@@ -172,8 +178,8 @@ def load_library() -> C.CDLL:
 EXPORTS = ('error create destroy parameter_count blocks shared_bytes set_weights get_weights get_optimizer_state '
            'set_optimizer_state memory set_data train get_training_losses training_versions pipeline_stats '
            'onecycle_point set_onecycle batch predict optimizer_test synchronize').split()
-EXTENSIONS = ('reference_config gpt_config parameter_count parameter_layout initialize_weights nccl_unique_id '
-              'stream sample train_mean_loss train_batch profile launch_count gemm weight_gradient_static attention_forward attention_backward '
+EXTENSIONS = ('reference_config gpt_config parameter_count parameter_layout initialize_weights config_digest nccl_unique_id '
+              'stream sample train_mean_loss train_batch profile launch_count read_activation selftest_bounded_wait gemm weight_gradient_static last_device_error attention_forward attention_backward '
               'cross_entropy').split()
 
 
@@ -280,6 +286,15 @@ class Native:
         self.check(self.lib.tg_ex_sample(self.handle, step, x.ctypes.data, y.ctypes.data))
         return x, y
 
+    def activation(self, layer, name):
+        """An activation of the last forward pass as FP32 [tokens, features] (diagnostic)."""
+        count = self.lib.tg_ex_read_activation(self.handle, layer, name.encode(), None, 0)
+        if count < 0:
+            raise RuntimeError(self.lib.tg_error().decode())
+        out = np.empty(count, np.float32)
+        self.check(self.lib.tg_ex_read_activation(self.handle, layer, name.encode(), out.ctypes.data, count))
+        return out.reshape(self.config.batch * self.config.context, -1)
+
     def memory_gb(self):
         used = C.c_double()
         self.check(self.lib.tg_memory(self.handle, C.byref(used)))
@@ -291,6 +306,25 @@ class Native:
         launches = (C.c_int64 * 32)()
         n = self.check(self.lib.tg_ex_profile(self.handle, names, ms, launches, 32, int(reset)))
         return {names[i].decode(): (ms[i], launches[i]) for i in range(n)}
+
+
+def require_matching_ranks(config: ConfigEx, all_gather) -> None:
+    """Refuses to go on unless every rank of the job holds the same configuration (apart from rank and
+    device).  ``all_gather(value: int) -> list[int]`` is the caller's own exchange (torch.distributed,
+    MPI, a file): it must return every rank's value, in rank order, on every rank.  Call it before
+    creating the engine: a communicator built from mismatched configurations hangs or trains garbage."""
+    lib = load_library()
+    digest = lib.tg_ex_config_digest(C.byref(config))
+    if not digest:
+        raise RuntimeError(lib.tg_error().decode())
+    digests = list(all_gather(int(digest)))
+    ranks = list(all_gather(int(config.rank)))
+    if len(digests) != config.world or sorted(ranks) != list(range(config.world)):
+        raise RuntimeError(f"data-parallel job: {len(digests)} ranks answered with ranks {ranks}, "
+                           f"this configuration says world {config.world}")
+    if len(set(digests)) != 1:
+        different = [r for r, d in enumerate(digests) if d != digests[0]]
+        raise RuntimeError(f"data-parallel job: ranks {different} hold a different configuration than rank 0")
 
 
 def initialize_weights(config: ConfigEx) -> np.ndarray:

@@ -11,7 +11,7 @@ PACKAGE = Path(__file__).resolve().parent
 CSRC = PACKAGE / "csrc"
 LIBRARY = PACKAGE / "libturbogpt_b200.so"
 SOURCES = ["host.cpp", "elementwise.cu", "attention_simt.cu", "gemm_simt.cu", "gemm_tc.cu", "attention_tc.cu", "optim.cu",
-           "engine.cu", "runtime.cu"]
+           "selftest.cu", "engine.cu", "runtime.cu"]
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
          "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=default", "--expt-relaxed-constexpr"]
 

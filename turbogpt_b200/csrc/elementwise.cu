@@ -642,39 +642,6 @@ void launch_swiglu_backward(Dtype t, const void *wide, const void *dout, void *d
     DISPATCH(t, (swiglu_backward_kernel<T><<<blocks_for(vectors, 256, 148 * 16), 256, 0, s>>>(
                     (const T *)wide, (const T *)dout, (T *)dwide, vectors, hidden / 8)));
 }
-template <class T> __global__ void gelu_kernel(const T *__restrict__ in, T *__restrict__ out, int64_t vectors) {
-    for (int64_t i = blockIdx.x * int64_t(blockDim.x) + threadIdx.x; i < vectors;
-         i += int64_t(gridDim.x) * blockDim.x) {
-        float v[8];
-        load8(in + i * 8, v);
-#pragma unroll
-        for (int j = 0; j < 8; ++j)
-            v[j] = gelu(v[j]);
-        store8(out + i * 8, v);
-    }
-}
-void launch_gelu(Dtype t, const void *in, void *out, int64_t count, cudaStream_t s) {
-    DISPATCH(t, (gelu_kernel<T><<<blocks_for(count / 8, 256, 148 * 16), 256, 0, s>>>((const T *)in, (T *)out,
-                                                                                 count / 8)));
-}
-template <class T>
-__global__ void gelu_backward_kernel(const T *__restrict__ pre, const T *__restrict__ dy, T *__restrict__ dx,
-                                     int64_t vectors) {
-    for (int64_t i = blockIdx.x * int64_t(blockDim.x) + threadIdx.x; i < vectors;
-         i += int64_t(gridDim.x) * blockDim.x) {
-        float v[8], g[8];
-        load8(pre + i * 8, v);
-        load8(dy + i * 8, g);
-#pragma unroll
-        for (int j = 0; j < 8; ++j)
-            g[j] *= gelu_derivative(v[j]);
-        store8(dx + i * 8, g);
-    }
-}
-void launch_gelu_backward(Dtype t, const void *pre, const void *dy, void *dx, int64_t count, cudaStream_t s) {
-    DISPATCH(t, (gelu_backward_kernel<T><<<blocks_for(count / 8, 256, 148 * 16), 256, 0, s>>>(
-                    (const T *)pre, (const T *)dy, (T *)dx, count / 8)));
-}
 
 // ------------------------------------------------------------------------------------------
 // 256-way softmax cross-entropy, one warp per row, 8 logits per lane (one 128-bit load):

@@ -181,7 +181,7 @@ void Engine::initialize() {
         allocate(muon_b, square, false);
         allocate(muon_sumsq, size_t(depth) * MuonBlocks);
     }
-    if (c.world > 1) {
+    if (c.world > 1 && !(c.flags & TG_FLAG_NO_COMMUNICATOR)) {
         const Nccl &nccl = Nccl::get();
         Nccl::UniqueId id;
         memcpy(id.internal, c.nccl_id, sizeof(id.internal));
@@ -220,6 +220,7 @@ void Engine::release() {
         cudaEventDestroy(exchange_done);
     for (void *p : allocations)
         cudaFree(p);
+    release_gemm_workspace(gemm_workspace);
     if (exchange_stream)
         cudaStreamDestroy(exchange_stream);
     if (stream)
@@ -269,7 +270,7 @@ void Engine::gemm(Family f, GemmArgs g) {
     g.in = act;
     run(f, [&] {
         if (tensor_cores && gemm_tc_supported(g))
-            launch_gemm_tc(g, sms, counters, stream);
+            launch_gemm_tc(g, sms, counters, stream, &gemm_workspace);
         else
             launch_gemm_simt(g, stream);
     });
@@ -547,7 +548,7 @@ void Engine::muon_family(int64_t first_offset, int rows, int cols) {
             run(FMuon, [&] {
                 g->in = Dtype::BF16;
                 if (tensor_cores && gemm_tc_supported(*g))
-                    launch_gemm_tc(*g, sms, counters, stream);
+                    launch_gemm_tc(*g, sms, counters, stream, &gemm_workspace);
                 else
                     launch_gemm_simt(*g, stream);
             });
@@ -615,6 +616,8 @@ void Engine::train(int steps) {
     if (!data || steps < 1 || steps > MaxLaunchSteps)
         throw std::runtime_error("Load data first; each invocation permits 1.." + std::to_string(MaxLaunchSteps) +
                                  " steps");
+    if (config.world > 1 && !comm)
+        throw std::runtime_error("This engine was created without a communicator: it cannot train on its own");
     if (step + uint64_t(steps) > uint64_t(INT32_MAX))
         throw std::runtime_error("Training step count exceeds signed 32-bit indexing");
     if (schedule && step + uint64_t(steps) > uint64_t(schedule_steps))
@@ -622,17 +625,17 @@ void Engine::train(int steps) {
     CHECK_CUDA(cudaMemsetAsync(&counters->iteration, 0, sizeof(int), stream));
     // A step reads everything that changes from device memory, so its kernel sequence is captured
     // once (after one eager step has sized every workspace) and replayed as a CUDA graph.
-    const bool use_graph = !profile && !comm && !(config.flags & TG_FLAG_NO_GRAPH) && !getenv("TURBOGPT_NO_GRAPH");
+    const bool use_graph = !profile && !comm && !(config.flags & TG_FLAG_NO_GRAPH);
     for (int i = 0; i < steps; ++i) {
         if (!use_graph || !graph_warm) {
             one_step(RunMode::Train);
             graph_warm = true;
             continue;
         }
-        if (step_graph && graph_generation != gemm_tc_workspace_generation())
+        if (step_graph && graph_generation != gemm_workspace.generation)
             drop_graph(); // the split-K workspace moved since the capture
         if (!step_graph) {
-            graph_generation = gemm_tc_workspace_generation();
+            graph_generation = gemm_workspace.generation;
             const int64_t before = launches;
             cudaGraph_t graph = nullptr;
             CHECK_CUDA(cudaStreamBeginCapture(stream, cudaStreamCaptureModeThreadLocal));
@@ -797,11 +800,64 @@ void Engine::get_optimizer_state(float *m, float *v, uint64_t *at_step) {
     *at_step = step;
 }
 
+// Diagnostic read-back of an activation the last forward pass saved (they are kept for backward).
+int64_t Engine::read_activation(int layer, const char *name, float *out, int64_t capacity) {
+    set_device();
+    const std::string which = name ? name : "";
+    const int W = config.width;
+    const void *source = nullptr;
+    int64_t columns = W;
+    if (layer < 0) {
+        if (which == "final_x")
+            source = final_x;
+        else if (which == "final_normed")
+            source = final_normed;
+    } else if (layer < int(layers.size())) {
+        const LayerActivations &a = layers[layer];
+        if (which == "x")
+            source = a.x;
+        else if (which == "normed1")
+            source = a.normed1;
+        else if (which == "qkv")
+            source = a.qkv, columns = 3 * W;
+        else if (which == "attended")
+            source = a.attended;
+        else if (which == "middle")
+            source = a.middle;
+        else if (which == "normed2")
+            source = a.normed2;
+        else if (which == "activated")
+            source = a.activated, columns = config.hidden;
+    }
+    if (!source)
+        throw std::runtime_error("Unknown activation '" + which + "' for layer " + std::to_string(layer));
+    const int64_t count = int64_t(tokens) * columns;
+    if (!out)
+        return count;
+    if (capacity < count)
+        throw std::runtime_error("Activation buffer too small");
+    if (act == Dtype::FP32) {
+        CHECK_CUDA(cudaMemcpyAsync(out, source, count * 4, cudaMemcpyDeviceToHost, stream));
+        CHECK_CUDA(cudaStreamSynchronize(stream));
+        return count;
+    }
+    std::vector<uint16_t> raw(count);
+    CHECK_CUDA(cudaMemcpyAsync(raw.data(), source, count * 2, cudaMemcpyDeviceToHost, stream));
+    CHECK_CUDA(cudaStreamSynchronize(stream));
+    for (int64_t i = 0; i < count; ++i) {
+        const uint32_t bits = uint32_t(raw[i]) << 16;
+        memcpy(out + i, &bits, 4);
+    }
+    return count;
+}
+
 // One optimizer step on bytes supplied by the caller instead of the resident corpus.
 void Engine::train_batch(const uint8_t *bx, const uint8_t *by, float *per_position) {
     set_device();
     if (!bx || !by)
         throw std::runtime_error("Missing batch input");
+    if (config.world > 1 && !comm)
+        throw std::runtime_error("This engine was created without a communicator: it cannot train on its own");
     if (schedule && step + 1 > uint64_t(schedule_steps))
         throw std::runtime_error("Training would exceed the OneCycle schedule");
     CHECK_CUDA(cudaMemcpyAsync(x, bx, tokens, cudaMemcpyHostToDevice, stream));

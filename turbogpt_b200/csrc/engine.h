@@ -89,6 +89,7 @@ struct Engine {
     double family_ms[FamilyCount] = {};
     int64_t family_launches[FamilyCount] = {};
     int64_t launches = 0, graph_launches = 0;
+    GemmWorkspace gemm_workspace; // this engine's split-K scratch (never shared with another engine or stream)
     cudaGraphExec_t step_graph = nullptr; // one captured training step
     bool graph_warm = false;
     int forward_batch = 0; // sequences the next forward pass covers (0: the configured batch)
@@ -118,6 +119,7 @@ struct Engine {
     float train_mean_loss(int steps);
     void train_batch(const uint8_t *bx, const uint8_t *by, float *per_position);
     void flush_profile();
+    int64_t read_activation(int layer, const char *name, float *out, int64_t capacity);
 
   private:
     void initialize();

@@ -3,19 +3,19 @@
 // (cuda/mma.cuh:69-108, cuda/ops.cuh:30-55,83-117) for every projection, input-gradient and
 // weight-gradient GEMM of the step.
 //
-// One persistent CTA per SM walks output tiles of 128 x BN (BN = 64..256).  Warp 0 streams
-// operand slices of 64 K-elements with TMA into a ring of 128-byte-swizzled shared-memory
-// stages; warp 1 issues tcgen05.mma (one thread) into one of two TMEM accumulators; warps 2-5
-// drain the other accumulator, so the epilogue of tile i overlaps the main loop of tile i+1.
-// Either operand may be K-major (row = 64 contiguous K elements) or MN-major (row = 64
-// contiguous M/N elements for one K index), which covers y = x W^T, dx = dy W and dW = dy^T x on
-// row-major tensors without transposes.
+// One persistent CTA per SM (or one CTA pair per two SMs, cta_group::2, for 256-row tiles) walks
+// output tiles of 128 x BN (BN = 64..256).  Warp 0 streams operand slices of 64 K-elements with
+// TMA into a ring of 128-byte-swizzled shared-memory stages; warp 1 issues tcgen05.mma (one
+// thread) into one of two 256-column TMEM accumulators; sixteen epilogue warps drain the other
+// accumulator, so the epilogue of tile i overlaps the main loop of tile i+1.  Either operand may be
+// K-major (row = 64 contiguous K elements) or MN-major (row = 64 contiguous M/N elements for one K
+// index), which covers y = x W^T, dx = dy W and dW = dy^T x on row-major tensors without transposes.
 //
-// Epilogue: each warp owns 32 rows.  Per 128-byte-wide chunk of its rows it reads the accumulator
-// (tcgen05.ld), optionally combines it with a tile of a second tensor fetched by TMA (residual,
-// pre-activation, or the Newton-Schulz operand), writes the result into a swizzled staging slot
-// and hands the slot to a TMA store: global reads and writes are whole 128-byte lines and the
-// tensor's edges are clipped by the TMA unit.
+// Epilogue: four warps share each 32-lane quarter of tensor memory and take every fourth
+// 32-column chunk.  A lane owns one output row: it reads its accumulator chunk (tcgen05.ld),
+// optionally combines it with the same chunk of a second tensor read straight from global memory
+// (residual, saved GELU derivative, or the Newton-Schulz operand) and writes 32-byte pieces with
+// 256-bit stores.
 //
 // Weight-gradient GEMMs have few output tiles and a very long K; they are split along K, each
 // split writes an FP32 partial tile to a workspace and the last split to finish a tile (an
@@ -36,7 +36,6 @@ constexpr int BM = 128, BK = 64, MaxBN = 256, MaxStages = 8;
 constexpr int StageABytes = BM * BK * 2;
 constexpr int EpilogueWarps = 16;
 constexpr int Threads = 64 + 32 * EpilogueWarps; // warp 0: TMA, warp 1: MMA, then the epilogue warps
-constexpr int SlotBytes = 32 * 128; // staging slot: 32 rows x 128 bytes
 constexpr int ControlBytes = 512;   // barriers, TMEM slot, flags
 constexpr int MaxShared = 232448 - 1024; // 227 KB less the runtime's own reservation
 constexpr int TmemColumns = 512;
@@ -47,7 +46,7 @@ struct TcParams {
     int a_mn, b_mn;         // operand majorness
     int splits, k_blocks_per_split;
     int epilogue, out_fp32;
-    int stages, slots;      // pipeline depth; (slots unused)
+    int stages;             // depth of the operand ring
     int wide;               // C, C2 and R rows are 32-byte aligned: 256-bit epilogue accesses
     void *c, *c2;
     const void *r;
@@ -103,15 +102,6 @@ __device__ __forceinline__ bool epilogue_all(bool ok) {
     return result != 0;
 }
 
-__device__ __forceinline__ uint4 load_shared16(uint32_t address) {
-    uint4 v;
-    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(address));
-    return v;
-}
-__device__ __forceinline__ void store_shared16(uint32_t address, uint4 v) {
-    asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(address), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
-                 : "memory");
-}
 // 32 bytes to or from global memory: one 256-bit access when `wide` (32-byte aligned), else two
 // 128-bit accesses; `second` says whether the upper half is inside the tensor.
 __device__ __forceinline__ void load_global32(const void *p, uint32_t (&r)[8], bool wide, bool second) {
@@ -137,24 +127,13 @@ __device__ __forceinline__ void store_global32(void *p, const uint32_t (&r)[8], 
             *(reinterpret_cast<uint4 *>(p) + 1) = make_uint4(r[4], r[5], r[6], r[7]);
     }
 }
-__device__ __forceinline__ void unpack8(uint4 u, float (&v)[8]) {
-    const unsigned w[4] = {u.x, u.y, u.z, u.w};
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        v[2 * i] = __uint_as_float(w[i] << 16);
-        v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
-    }
-}
-
 // Pair = true: the CTA is half of a cluster of two that computes a 256-row tile with
 // cta_group::2 MMAs issued by the pair's first CTA.  Each CTA stages its own 128 rows of A and half
 // of the B tile (the tensor core reads the other half from the partner's shared memory), so a
 // K block costs each SM 16 KB + BN/2 x 128 B instead of 16 KB + BN x 128 B and the ring is deeper.
 template <int Kind, bool OutFp32, bool Pair>
 __global__ void __launch_bounds__(Threads, 1)
-gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-               const __grid_constant__ CUtensorMap map_c, const __grid_constant__ CUtensorMap map_c2,
-               const __grid_constant__ CUtensorMap map_r, TcParams p) {
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, TcParams p) {
     extern __shared__ uint8_t raw_shared[];
     const uint32_t base = (smem_address(raw_shared) + 1023u) & ~1023u;
     uint8_t *aligned = raw_shared + (base - smem_address(raw_shared));
@@ -162,11 +141,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const uint32_t rank = Pair ? cluster_rank() : 0u;
     const int bn_local = p.bn / Unit; // B rows staged by this CTA
     const int stage_bytes = StageABytes + bn_local * BK * 2;
-    uint64_t *barriers = reinterpret_cast<uint64_t *>(aligned + p.stages * stage_bytes + 4 * p.slots * SlotBytes);
-    // barrier slots: full[8], empty[8], tmem_full[2], tmem_empty[2], r_full[4 warps][4 slots]
+    uint64_t *barriers = reinterpret_cast<uint64_t *>(aligned + p.stages * stage_bytes);
+    // barriers: full[8], empty[8], tmem_full[2], tmem_empty[2]
     const uint32_t full0 = smem_address(barriers), empty0 = full0 + 8 * MaxStages, tfull0 = empty0 + 8 * MaxStages,
-                   tempty0 = tfull0 + 16, rfull0 = tempty0 + 16;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(barriers + 2 * MaxStages + 4 + 16);
+                   tempty0 = tfull0 + 16;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(barriers + 2 * MaxStages + 4);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
     volatile int *last_split_flag = reinterpret_cast<volatile int *>(tmem_slot + 2);
 
@@ -180,13 +159,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             mbarrier_init(tfull0 + 8 * b, 1);
             mbarrier_init(tempty0 + 8 * b, EpilogueWarps * Unit);
         }
-        for (int i = 0; i < 16; ++i)
-            mbarrier_init(rfull0 + 8 * i, 1);
         *abort_flag = 0;
         fence_barrier_init();
         prefetch_map(&map_a);
         prefetch_map(&map_b);
-        prefetch_map(&map_c);
     }
     if (warp == 1) {
         if constexpr (Pair) {
@@ -537,45 +513,190 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     }
 }
 
-struct Workspace {
-    float *partials = nullptr;
-    unsigned *tickets = nullptr;
-    size_t partial_bytes = 0, ticket_count = 0;
+// ---------------------------------------------------------------------------- host side ------
+struct Schedule {
+    int bn = 0, splits = 1, k_blocks_per_split = 0, pair = 0;
 };
-std::mutex workspace_mutex;
-std::unordered_map<int, Workspace> workspaces; // per device
-std::atomic<uint64_t> workspace_generation{1};
 
-// Split-K workspace, grown on demand outside stream capture; one per device, shared by the
-// engine's single stream.
-Workspace &workspace_for(size_t partial_bytes, size_t tickets, cudaStream_t s) {
-    int device = 0;
-    CHECK_CUDA(cudaGetDevice(&device));
-    std::lock_guard<std::mutex> lock(workspace_mutex);
-    Workspace &w = workspaces[device];
-    if (w.partial_bytes < partial_bytes) {
+// Tile width, K splits and single CTA / CTA pair by a small cost model, in clocks per 64-deep K
+// block: the MMA takes bn/2, the shared-memory operand reads (128+bn)/4; a tile adds a fixed drain
+// cost and every split one pass over the FP32 partial tile.  CTA pairs (256-row tiles) are tried
+// first: they halve the B bytes each SM stages per K block.
+Schedule choose_schedule(const GemmArgs &g, int sms) {
+    const bool b_mn = g.b_col != 1;
+    const bool second_tensor = g.epilogue != Epilogue::Store;
+    const int m_tiles = (g.m + BM - 1) / BM, k_blocks = (g.k + BK - 1) / BK;
+    Schedule best;
+    long long best_time = 0;
+    for (int unit : {2, 1}) {
+        if (unit == 2 && (m_tiles < 2 || sms < 2))
+            continue;
+        const int slots = sms / unit;
+        const long long m_units = (m_tiles + unit - 1) / unit;
+        for (int bn : {256, 192, 128, 64}) {
+            if (bn > 64 && bn - 64 >= g.n)
+                continue; // a narrower tile already covers N
+            if (unit == 2 && (bn == 64 || (b_mn && bn == 192)))
+                continue; // each CTA stages bn/2 rows of B: whole 64-row blocks when B is MN-major
+            const long long tiles = m_units * ((g.n + bn - 1) / bn) * g.batch;
+            // Clocks per K block and CTA: the MMA takes bn/2; a single CTA cannot keep its ring full
+            // (measured ~65 % of that rate), a pair can.
+            const int mma = bn / 2 > (128 + bn) / 4 ? bn / 2 : (128 + bn) / 4;
+            const int block_cost = unit == 2 ? mma + 16 : mma * (k_blocks >= 64 ? 9 : 11) / 8 + 16;
+            for (int splits : {1, 2, 3, 4, 6, 8, 12, 16}) {
+                if (splits > 1 && (k_blocks / splits < 8 || tiles * splits > slots || second_tensor))
+                    continue;
+                const int per = (k_blocks + splits - 1) / splits;
+                if (splits > 1 && (k_blocks + per - 1) / per != splits)
+                    continue; // would leave an empty split
+                const long long rounds = (tiles * splits + slots - 1) / slots;
+                const long long time = rounds * ((long long)per * block_cost + bn + (splits > 1 ? splits * bn / 2 : 0));
+                if (!best.bn || time < best_time)
+                    best.bn = bn, best.splits = splits, best.k_blocks_per_split = per, best.pair = unit == 2,
+                    best_time = time;
+            }
+        }
+    }
+    return best;
+}
+
+// Scratch a schedule needs: FP32 partial tiles and one ticket per output tile (none without a K split).
+struct ScratchNeed {
+    size_t partial_bytes = 0, tickets = 0;
+};
+ScratchNeed scratch_need(const GemmArgs &g, const Schedule &sc) {
+    if (sc.splits <= 1)
+        return {};
+    const int unit = sc.pair ? 2 : 1;
+    const int m_tiles = (g.m + BM - 1) / BM, padded_m_tiles = (m_tiles + unit - 1) / unit * unit;
+    const int n_tiles = (g.n + sc.bn - 1) / sc.bn;
+    return {size_t(sc.splits) * g.batch * padded_m_tiles * BM * n_tiles * sc.bn * sizeof(float),
+            size_t(padded_m_tiles) * n_tiles * g.batch};
+}
+
+// Stand-alone calls (tg_ex_gemm) share one workspace per device, grown on demand.
+std::mutex shared_workspace_mutex;
+std::unordered_map<int, GemmWorkspace> shared_workspaces;
+
+void grow(GemmWorkspace &w, const ScratchNeed &need, cudaStream_t s) {
+    if (!w.error_word) {
+        CHECK_CUDA(cudaMalloc(&w.error_word, sizeof(StepCounters)));
+        CHECK_CUDA(cudaMemset(w.error_word, 0, sizeof(StepCounters)));
+    }
+    if (w.partial_bytes < need.partial_bytes) {
         CHECK_CUDA(cudaStreamSynchronize(s));
         if (w.partials)
             CHECK_CUDA(cudaFree(w.partials));
-        CHECK_CUDA(cudaMalloc(&w.partials, partial_bytes));
-        ++workspace_generation;
-        w.partial_bytes = partial_bytes;
+        w.partials = nullptr, w.partial_bytes = 0;
+        CHECK_CUDA(cudaMalloc(&w.partials, need.partial_bytes));
+        w.partial_bytes = need.partial_bytes;
+        ++w.generation;
     }
-    if (w.ticket_count < tickets) {
+    if (w.ticket_count < need.tickets) {
         CHECK_CUDA(cudaStreamSynchronize(s));
         if (w.tickets)
             CHECK_CUDA(cudaFree(w.tickets));
-        CHECK_CUDA(cudaMalloc(&w.tickets, tickets * sizeof(unsigned)));
-        CHECK_CUDA(cudaMemset(w.tickets, 0, tickets * sizeof(unsigned)));
-        ++workspace_generation;
-        w.ticket_count = tickets;
+        w.tickets = nullptr, w.ticket_count = 0;
+        CHECK_CUDA(cudaMalloc(&w.tickets, need.tickets * sizeof(unsigned)));
+        CHECK_CUDA(cudaMemset(w.tickets, 0, need.tickets * sizeof(unsigned)));
+        w.ticket_count = need.tickets;
+        ++w.generation;
     }
-    return w;
+}
+
+// Builds the kernel parameters and tensor maps for `sc` and launches.  `partials` / `tickets` may be
+// null when the schedule does not split K.
+void launch_schedule(const GemmArgs &g, const Schedule &sc, int sms, float *partials, unsigned *tickets,
+                     StepCounters *counters, cudaStream_t s) {
+    TcParams p{};
+    p.m = g.m, p.n = g.n, p.k = g.k, p.batch = g.batch;
+    p.a_mn = g.a_col == 1 ? 0 : 1;
+    p.b_mn = g.b_col == 1 ? 0 : 1;
+    p.epilogue = int(g.epilogue), p.out_fp32 = g.out == Dtype::FP32;
+    p.bn = sc.bn, p.splits = sc.splits, p.k_blocks_per_split = sc.k_blocks_per_split;
+    const int64_t lda = p.a_mn ? g.a_col : g.a_row, ldb = p.b_mn ? g.b_col : g.b_row;
+    const int unit = sc.pair ? 2 : 1;
+    const int m_tiles = (g.m + BM - 1) / BM, padded_m_tiles = (m_tiles + unit - 1) / unit * unit;
+    const int n_tiles = (g.n + p.bn - 1) / p.bn;
+    const long long tiles = (long long)(padded_m_tiles / unit) * n_tiles * g.batch; // scheduling units
+    const int bn_local = p.bn / unit;
+    const int stage_bytes = StageABytes + bn_local * BK * 2;
+    p.stages = (MaxShared - 1024 - ControlBytes) / stage_bytes;
+    if (p.stages > MaxStages)
+        p.stages = MaxStages;
+    const int shared = p.stages * stage_bytes + ControlBytes + 1024;
+    p.c = g.c, p.c2 = g.c2, p.r = g.r;
+    p.ldc = g.ldc, p.ldr = g.ldr, p.c_batch = g.c_batch, p.r_batch = g.r_batch;
+    p.alpha = g.alpha, p.beta = g.beta;
+    p.counters = counters;
+    p.workspace = partials, p.tickets = tickets;
+    {
+        const int per32 = p.out_fp32 ? 8 : 16; // elements per 32 bytes
+        auto aligned32 = [&](const void *ptr, int64_t ld, int64_t batch_stride) {
+            return !ptr || (reinterpret_cast<uintptr_t>(ptr) % 32 == 0 && ld % per32 == 0 && batch_stride % per32 == 0);
+        };
+        p.wide = aligned32(g.c, g.ldc, g.c_batch) && aligned32(g.c2, g.ldc, g.c_batch) &&
+                 aligned32(g.r, g.ldr, g.r_batch);
+    }
+    CUtensorMap map_a = p.a_mn ? make_map_bf16(g.a, g.m, g.k, g.batch, lda, g.a_batch, 64, BK)
+                               : make_map_bf16(g.a, g.k, g.m, g.batch, lda, g.a_batch, BK, BM);
+    CUtensorMap map_b = p.b_mn ? make_map_bf16(g.b, g.n, g.k, g.batch, ldb, g.b_batch, 64, BK)
+                               : make_map_bf16(g.b, g.k, g.n, g.batch, ldb, g.b_batch, BK, bn_local);
+    const long long work = tiles * p.splits;
+    const int slots = sms / unit;
+    const int grid = int(work < slots ? work : slots) * unit;
+    auto launch = [&](auto kernel) {
+        // The opt-in shared-memory size is an attribute of each instantiation on each device.
+        static std::mutex guard;
+        static std::unordered_map<const void *, unsigned long long> configured; // kernel -> device bit mask
+        int device = 0;
+        CHECK_CUDA(cudaGetDevice(&device));
+        {
+            std::lock_guard<std::mutex> lock(guard);
+            unsigned long long &mask = configured[reinterpret_cast<const void *>(kernel)];
+            if (!(mask >> (device & 63) & 1ull)) {
+                CHECK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, MaxShared));
+                mask |= 1ull << (device & 63);
+            }
+        }
+        cudaLaunchConfig_t config{};
+        config.gridDim = dim3(grid), config.blockDim = dim3(Threads);
+        config.dynamicSmemBytes = shared, config.stream = s;
+        cudaLaunchAttribute attributes[2]{};
+        attributes[0].id = cudaLaunchAttributeClusterDimension;
+        attributes[0].val.clusterDim.x = unit, attributes[0].val.clusterDim.y = 1, attributes[0].val.clusterDim.z = 1;
+        // The kernel's set-up (barriers, tensor memory, descriptors) overlaps the tail of the kernel before it.
+        attributes[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attributes[1].val.programmaticStreamSerializationAllowed = 1;
+        config.attrs = attributes, config.numAttrs = 2;
+        CHECK_CUDA(cudaLaunchKernelEx(&config, kernel, map_a, map_b, p));
+    };
+    auto launch_kind = [&](auto pair_tag) {
+        constexpr bool P = decltype(pair_tag)::value;
+        if (p.out_fp32) {
+            if (g.epilogue == Epilogue::Axpby)
+                launch(gemm_tc_kernel<int(Epilogue::Axpby), true, P>);
+            else
+                launch(gemm_tc_kernel<int(Epilogue::Store), true, P>);
+        } else {
+            switch (g.epilogue) {
+            case Epilogue::Store: launch(gemm_tc_kernel<int(Epilogue::Store), false, P>); break;
+            case Epilogue::Residual: launch(gemm_tc_kernel<int(Epilogue::Residual), false, P>); break;
+            case Epilogue::GeluDual: launch(gemm_tc_kernel<int(Epilogue::GeluDual), false, P>); break;
+            case Epilogue::GeluGrad: launch(gemm_tc_kernel<int(Epilogue::GeluGrad), false, P>); break;
+            case Epilogue::Axpby: launch(gemm_tc_kernel<int(Epilogue::Axpby), false, P>); break;
+            }
+        }
+    };
+    if (sc.pair)
+        launch_kind(std::true_type{});
+    else
+        launch_kind(std::false_type{});
+    CHECK_CUDA(cudaGetLastError());
 }
 } // namespace
 
 int gemm_tc_shared_bytes() { return MaxShared; }
-uint64_t gemm_tc_workspace_generation() { return workspace_generation.load(); }
 
 bool gemm_tc_supported(const GemmArgs &g) {
     if (g.in != Dtype::BF16)
@@ -599,145 +720,34 @@ bool gemm_tc_supported(const GemmArgs &g) {
     return true;
 }
 
-void launch_gemm_tc(const GemmArgs &g, int sms, StepCounters *counters, cudaStream_t s) {
-    TcParams p{};
-    p.m = g.m, p.n = g.n, p.k = g.k, p.batch = g.batch;
-    p.a_mn = g.a_col == 1 ? 0 : 1;
-    p.b_mn = g.b_col == 1 ? 0 : 1;
-    p.epilogue = int(g.epilogue), p.out_fp32 = g.out == Dtype::FP32;
-    const bool second_tensor = g.epilogue != Epilogue::Store;
-    p.slots = 0;
-    const int64_t lda = p.a_mn ? g.a_col : g.a_row, ldb = p.b_mn ? g.b_col : g.b_row;
-    const int m_tiles = (g.m + BM - 1) / BM, k_blocks = (g.k + BK - 1) / BK;
-    // Tile width and K splits by a small cost model, in clocks per 64-deep K block: the MMA
-    // takes bn/2, the shared-memory operand reads (128+bn)/4; a tile adds a fixed drain cost and
-    // every split one pass over the FP32 partial tile.  Four staging slots leave room for 192 columns.
-    // CTA pairs (256-row tiles) are tried first: they halve the B bytes each SM stages per K block.
-    // TURBOGPT_GEMM_PAIR=0 / 1 forces one form (for measurements).
-    static const int forced_pair = [] {
-        const char *v = getenv("TURBOGPT_GEMM_PAIR");
-        return v ? atoi(v) : -1;
-    }();
-    long long best_time = 0;
-    p.bn = 0;
-    int pair = 0;
-    for (int unit : {2, 1}) {
-        if ((unit == 2 && (forced_pair == 0 || m_tiles < 2 || sms < 2)) || (unit == 1 && forced_pair == 1 && p.bn))
-            continue;
-        const int slots = sms / unit;
-        const long long m_units = (m_tiles + unit - 1) / unit;
-        for (int bn : {256, 192, 128, 64}) {
-            if (bn > 64 && bn - 64 >= g.n)
-                continue; // a narrower tile already covers N
-            if (unit == 2 && (bn == 64 || (p.b_mn && bn == 192)))
-                continue; // each CTA stages bn/2 rows of B: whole 64-row blocks when B is MN-major
-            const long long tiles = m_units * ((g.n + bn - 1) / bn) * g.batch;
-            // Clocks per K block and CTA: the MMA takes bn/2; a single CTA cannot keep its ring full
-            // (measured ~65 % of that rate), a pair can.
-            const int mma = bn / 2 > (128 + bn) / 4 ? bn / 2 : (128 + bn) / 4;
-            const int block_cost = unit == 2 ? mma + 16 : mma * (k_blocks >= 64 ? 9 : 11) / 8 + 16;
-            for (int splits : {1, 2, 3, 4, 6, 8, 12, 16}) {
-                if (splits > 1 && (k_blocks / splits < 8 || tiles * splits > slots || second_tensor))
-                    continue;
-                const int per = (k_blocks + splits - 1) / splits;
-                if (splits > 1 && (k_blocks + per - 1) / per != splits)
-                    continue; // would leave an empty split
-                const long long rounds = (tiles * splits + slots - 1) / slots;
-                const long long time = rounds * ((long long)per * block_cost + bn + (splits > 1 ? splits * bn / 2 : 0));
-                if (!p.bn || time < best_time)
-                    p.bn = bn, p.splits = splits, p.k_blocks_per_split = per, best_time = time, pair = unit == 2;
-            }
-        }
+void release_gemm_workspace(GemmWorkspace &w) {
+    if (w.partials)
+        cudaFree(w.partials);
+    if (w.tickets)
+        cudaFree(w.tickets);
+    if (w.error_word)
+        cudaFree(w.error_word);
+    w = GemmWorkspace{};
+}
+
+// `workspace`: the caller's own split-K scratch (an Engine's: grown here, outside stream capture,
+// when a schedule needs more); nullptr: the per-device workspace shared by the stand-alone calls,
+// whose device-side give-ups are reported by gemm_tc_take_device_error().
+void launch_gemm_tc(const GemmArgs &g, int sms, StepCounters *counters, cudaStream_t s, GemmWorkspace *workspace) {
+    const Schedule sc = choose_schedule(g, sms);
+    const ScratchNeed need = scratch_need(g, sc);
+    if (workspace) {
+        if (need.partial_bytes > workspace->partial_bytes || need.tickets > workspace->ticket_count || !workspace->error_word)
+            grow(*workspace, need, s);
+        launch_schedule(g, sc, sms, workspace->partials, workspace->tickets, counters, s);
+        return;
     }
-    static const bool trace = getenv("TURBOGPT_GEMM_TRACE") != nullptr; // prints every schedule chosen
-    if (trace)
-        fprintf(stderr, "gemm %d x %d x %d batch %d a_mn %d b_mn %d epilogue %d: bn %d splits %d pair %d\n", g.m, g.n,
-                g.k, g.batch, p.a_mn, p.b_mn, p.epilogue, p.bn, p.splits, pair);
-    const int unit = pair ? 2 : 1;
-    const int padded_m_tiles = (m_tiles + unit - 1) / unit * unit;
-    const int n_tiles = (g.n + p.bn - 1) / p.bn;
-    const long long tiles = (long long)(padded_m_tiles / unit) * n_tiles * g.batch; // scheduling units
-    const int bn_local = p.bn / unit;
-    const int stage_bytes = StageABytes + bn_local * BK * 2;
-    p.stages = (MaxShared - 1024 - ControlBytes) / stage_bytes;
-    if (p.stages > MaxStages)
-        p.stages = MaxStages;
-    const int shared = p.stages * stage_bytes + ControlBytes + 1024;
-    p.c = g.c, p.c2 = g.c2, p.r = g.r;
-    p.ldc = g.ldc, p.ldr = g.ldr, p.c_batch = g.c_batch, p.r_batch = g.r_batch;
-    p.alpha = g.alpha, p.beta = g.beta;
-    p.counters = counters;
-    {
-        const int per32 = p.out_fp32 ? 8 : 16; // elements per 32 bytes
-        auto aligned32 = [&](const void *ptr, int64_t ld, int64_t batch_stride) {
-            return !ptr || (reinterpret_cast<uintptr_t>(ptr) % 32 == 0 && ld % per32 == 0 && batch_stride % per32 == 0);
-        };
-        p.wide = aligned32(g.c, g.ldc, g.c_batch) && aligned32(g.c2, g.ldc, g.c_batch) &&
-                 aligned32(g.r, g.ldr, g.r_batch);
-    }
-    if (p.splits > 1) {
-        size_t bytes = size_t(p.splits) * g.batch * padded_m_tiles * BM * n_tiles * p.bn * sizeof(float);
-        Workspace &w = workspace_for(bytes, size_t(tiles) * unit, s);
-        p.workspace = w.partials;
-        p.tickets = w.tickets;
-    }
-    CUtensorMap map_a = p.a_mn ? make_map_bf16(g.a, g.m, g.k, g.batch, lda, g.a_batch, 64, BK)
-                               : make_map_bf16(g.a, g.k, g.m, g.batch, lda, g.a_batch, BK, BM);
-    CUtensorMap map_b = p.b_mn ? make_map_bf16(g.b, g.n, g.k, g.batch, ldb, g.b_batch, 64, BK)
-                               : make_map_bf16(g.b, g.k, g.n, g.batch, ldb, g.b_batch, BK, bn_local);
-    const int element = p.out_fp32 ? 4 : 2;
-    CUtensorMap map_c = make_map(g.c, element, g.n, g.m, g.batch, g.ldc, g.c_batch, 128 / element, 32);
-    long long work = tiles * p.splits;
-    const int slots = sms / unit;
-    int grid = int(work < slots ? work : slots) * unit;
-    auto launch = [&](auto kernel) {
-        // The opt-in shared-memory size is an attribute of each instantiation on each device.
-        static std::mutex guard;
-        static std::unordered_map<const void *, unsigned long long> configured; // kernel -> device bit mask
-        int device = 0;
-        CHECK_CUDA(cudaGetDevice(&device));
-        {
-            std::lock_guard<std::mutex> lock(guard);
-            unsigned long long &mask = configured[reinterpret_cast<const void *>(kernel)];
-            if (!(mask >> (device & 63) & 1ull)) {
-                CHECK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, MaxShared));
-                mask |= 1ull << (device & 63);
-            }
-        }
-        cudaLaunchConfig_t config{};
-        config.gridDim = dim3(grid), config.blockDim = dim3(Threads);
-        config.dynamicSmemBytes = shared, config.stream = s;
-        static const bool programmatic = getenv("TURBOGPT_NO_PDL") == nullptr;
-        cudaLaunchAttribute attributes[2]{};
-        attributes[0].id = cudaLaunchAttributeClusterDimension;
-        attributes[0].val.clusterDim.x = unit, attributes[0].val.clusterDim.y = 1, attributes[0].val.clusterDim.z = 1;
-        attributes[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-        attributes[1].val.programmaticStreamSerializationAllowed = 1;
-        config.attrs = attributes, config.numAttrs = programmatic ? 2 : 1;
-        CHECK_CUDA(cudaLaunchKernelEx(&config, kernel, map_a, map_b, map_c, map_c, map_c, p));
-    };
-    auto launch_kind = [&](auto pair_tag) {
-        constexpr bool P = decltype(pair_tag)::value;
-        if (p.out_fp32) {
-            if (g.epilogue == Epilogue::Axpby)
-                launch(gemm_tc_kernel<int(Epilogue::Axpby), true, P>);
-            else
-                launch(gemm_tc_kernel<int(Epilogue::Store), true, P>);
-        } else {
-            switch (g.epilogue) {
-            case Epilogue::Store: launch(gemm_tc_kernel<int(Epilogue::Store), false, P>); break;
-            case Epilogue::Residual: launch(gemm_tc_kernel<int(Epilogue::Residual), false, P>); break;
-            case Epilogue::GeluDual: launch(gemm_tc_kernel<int(Epilogue::GeluDual), false, P>); break;
-            case Epilogue::GeluGrad: launch(gemm_tc_kernel<int(Epilogue::GeluGrad), false, P>); break;
-            case Epilogue::Axpby: launch(gemm_tc_kernel<int(Epilogue::Axpby), false, P>); break;
-            }
-        }
-    };
-    if (pair)
-        launch_kind(std::true_type{});
-    else
-        launch_kind(std::false_type{});
-    CHECK_CUDA(cudaGetLastError());
+    int device = 0;
+    CHECK_CUDA(cudaGetDevice(&device));
+    std::lock_guard<std::mutex> lock(shared_workspace_mutex);
+    GemmWorkspace &w = shared_workspaces[device];
+    grow(w, need, s);
+    launch_schedule(g, sc, sms, w.partials, w.tickets, counters ? counters : w.error_word, s);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -745,8 +755,8 @@ void launch_gemm_tc(const GemmArgs &g, int sms, StepCounters *counters, cudaStre
 // need a gradient: a serving or training process that has handed the whole device to its own
 // memory pool, a caller inside a region where the allocator's implicit device synchronisation is
 // not acceptable, or one whose memory budget was fixed when the process started.  For them the
-// split-K scratch (FP32 partial tiles and the per-tile tickets) lives in the array below, which
-// every GPU that loads this library holds until the process exits.
+// split-K scratch (FP32 partial tiles, the per-tile tickets and a device error word) lives in the
+// array below, which every GPU that loads this library holds until the process exits.
 //
 // In host code `static_scratch` is only a stand-in for the symbol: its device address comes from
 // cudaGetSymbolAddress, fetched once per device with that device current, on the first call for
@@ -754,11 +764,15 @@ void launch_gemm_tc(const GemmArgs &g, int sms, StepCounters *counters, cudaStre
 // array and it keeps the previous call's contents: the tickets are cleared on the stream before
 // every launch, the partial tiles are fully overwritten before they are read.  Two calls that
 // overlap on the GPU (different streams, or different threads) race on it.
+//
+// The schedule (tile width, K splits, CTA pair) and the kernel are exactly those tg_ex_gemm uses
+// for the same shape, so the results are bit-identical to it.
 // ------------------------------------------------------------------------------------------
 namespace {
 constexpr size_t StaticPartialBytes = size_t(16) << 20; // 16 MiB of FP32 partial tiles
 constexpr int StaticTickets = 1024;                      // output tiles
-static __device__ __align__(256) unsigned char static_scratch[StaticPartialBytes + StaticTickets * sizeof(unsigned)];
+constexpr size_t StaticErrorOffset = StaticPartialBytes + StaticTickets * sizeof(unsigned);
+static __device__ __align__(256) unsigned char static_scratch[StaticErrorOffset + 256];
 void *static_scratch_address[64] = {}; // per device, filled on first use
 } // namespace
 
@@ -778,58 +792,54 @@ void launch_weight_gradient_static(const void *dy, const void *x, float *dw, int
     CHECK_CUDA(cudaGetDevice(&device));
     if (device < 0 || device >= 64)
         throw std::runtime_error("weight gradient: device index out of range");
-    auto kernel = gemm_tc_kernel<int(Epilogue::Store), true, false>;
     if (!static_scratch_address[device]) { // set-up, once per device, with that device current
         void *address = nullptr;
         CHECK_CUDA(cudaGetSymbolAddress(&address, static_scratch));
-        CHECK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, MaxShared));
+        CHECK_CUDA(cudaMemsetAsync(static_cast<unsigned char *>(address) + StaticErrorOffset, 0, 256, s));
         static_scratch_address[device] = address;
     }
-    TcParams p{};
-    p.m = g.m, p.n = g.n, p.k = g.k, p.batch = 1;
-    p.a_mn = 1, p.b_mn = 1, p.epilogue = int(Epilogue::Store), p.out_fp32 = 1;
-    const int m_tiles = (g.m + BM - 1) / BM, k_blocks = (g.k + BK - 1) / BK;
-    long long best_time = 0;
-    for (int bn : {256, 192, 128, 64}) { // same cost model as launch_gemm_tc
-        if (bn > 64 && bn - 64 >= g.n)
+    const Schedule sc = choose_schedule(g, sms);
+    const ScratchNeed need = scratch_need(g, sc);
+    if (need.partial_bytes > StaticPartialBytes || need.tickets > size_t(StaticTickets))
+        throw std::runtime_error("weight gradient: this shape needs " + std::to_string(need.partial_bytes) +
+                                 " bytes of scratch in " + std::to_string(need.tickets) +
+                                 " tiles; the built-in array holds " + std::to_string(StaticPartialBytes) +
+                                 " bytes and " + std::to_string(StaticTickets) + " tiles (use tg_ex_gemm, which allocates)");
+    unsigned char *scratch = static_cast<unsigned char *>(static_scratch_address[device]);
+    unsigned *tickets = reinterpret_cast<unsigned *>(scratch + StaticPartialBytes);
+    CHECK_CUDA(cudaMemsetAsync(tickets, 0, StaticTickets * sizeof(unsigned), s)); // must start at zero
+    launch_schedule(g, sc, sms, reinterpret_cast<float *>(scratch), tickets,
+                    reinterpret_cast<StepCounters *>(scratch + StaticErrorOffset), s);
+}
+
+// First device-side give-up code recorded by the stand-alone GEMM calls (tg_ex_gemm,
+// tg_ex_weight_gradient_static) on the current device since the last query; 0 when none.
+// Synchronises `s`; allocates nothing.
+int gemm_tc_take_device_error(cudaStream_t s) {
+    int device = 0;
+    CHECK_CUDA(cudaGetDevice(&device));
+    CHECK_CUDA(cudaStreamSynchronize(s));
+    StepCounters *words[2] = {nullptr, nullptr};
+    {
+        std::lock_guard<std::mutex> lock(shared_workspace_mutex);
+        auto found = shared_workspaces.find(device);
+        if (found != shared_workspaces.end())
+            words[0] = found->second.error_word;
+    }
+    if (device >= 0 && device < 64 && static_scratch_address[device])
+        words[1] = reinterpret_cast<StepCounters *>(static_cast<unsigned char *>(static_scratch_address[device]) +
+                                                    StaticErrorOffset);
+    int code = 0;
+    for (StepCounters *word : words) {
+        if (!word)
             continue;
-        const long long tiles = (long long)m_tiles * ((g.n + bn - 1) / bn);
-        const int block_cost = bn / 2 > (128 + bn) / 4 ? bn / 2 : (128 + bn) / 4;
-        for (int splits : {1, 2, 3, 4, 6, 8, 12, 16}) {
-            if (splits > 1 && (k_blocks / splits < 8 || tiles * splits > sms))
-                continue;
-            const int per = (k_blocks + splits - 1) / splits;
-            if (splits > 1 && (k_blocks + per - 1) / per != splits)
-                continue;
-            const long long rounds = (tiles * splits + sms - 1) / sms;
-            const long long time = rounds * ((long long)per * (block_cost + 16) + bn + (splits > 1 ? splits * bn / 2 : 0));
-            if (!p.bn || time < best_time)
-                p.bn = bn, p.splits = splits, p.k_blocks_per_split = per, best_time = time;
+        StepCounters host{};
+        CHECK_CUDA(cudaMemcpy(&host, word, sizeof(host), cudaMemcpyDeviceToHost));
+        if (host.error) {
+            if (!code)
+                code = host.error;
+            CHECK_CUDA(cudaMemset(word, 0, sizeof(StepCounters)));
         }
     }
-    const int n_tiles = (g.n + p.bn - 1) / p.bn;
-    const long long tiles = (long long)m_tiles * n_tiles;
-    const size_t needed = p.splits > 1 ? size_t(p.splits) * m_tiles * BM * n_tiles * p.bn * sizeof(float) : 0;
-    if (needed > StaticPartialBytes || (p.splits > 1 && tiles > StaticTickets))
-        throw std::runtime_error("weight gradient: this shape needs " + std::to_string(needed) + " bytes of scratch in " +
-                                 std::to_string(tiles) + " tiles; the built-in array holds " +
-                                 std::to_string(StaticPartialBytes) + " bytes and " + std::to_string(StaticTickets) +
-                                 " tiles (use tg_ex_gemm, which allocates)");
-    const int stage_bytes = StageABytes + p.bn * BK * 2;
-    p.stages = (MaxShared - 1024 - ControlBytes) / stage_bytes;
-    if (p.stages > MaxStages)
-        p.stages = MaxStages;
-    const int shared = p.stages * stage_bytes + ControlBytes + 1024;
-    p.c = g.c, p.ldc = g.ldc, p.alpha = 1.f, p.beta = 0.f;
-    p.wide = reinterpret_cast<uintptr_t>(g.c) % 32 == 0 && g.ldc % 8 == 0;
-    unsigned char *scratch = static_cast<unsigned char *>(static_scratch_address[device]);
-    p.workspace = reinterpret_cast<float *>(scratch);
-    p.tickets = reinterpret_cast<unsigned *>(scratch + StaticPartialBytes);
-    CHECK_CUDA(cudaMemsetAsync(p.tickets, 0, StaticTickets * sizeof(unsigned), s)); // must start at zero
-    CUtensorMap map_a = make_map_bf16(g.a, g.m, g.k, 1, g.a_col, 0, 64, BK);
-    CUtensorMap map_b = make_map_bf16(g.b, g.n, g.k, 1, g.b_col, 0, 64, BK);
-    CUtensorMap map_c = make_map(g.c, 4, g.n, g.m, 1, g.ldc, 0, 32, 32);
-    const long long work = tiles * p.splits;
-    kernel<<<int(work < sms ? work : sms), Threads, shared, s>>>(map_a, map_b, map_c, map_c, map_c, p);
-    CHECK_CUDA(cudaGetLastError());
+    return code;
 }

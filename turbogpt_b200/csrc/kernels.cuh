@@ -116,9 +116,6 @@ void launch_swiglu(Dtype t, const void *wide, void *out, int tokens, int hidden,
 // dwide = d(gate | up) from dout, recomputing the activation with the forward's roundings.
 void launch_swiglu_backward(Dtype t, const void *wide, const void *dout, void *dwide, int tokens, int hidden,
                             cudaStream_t s);
-void launch_gelu(Dtype t, const void *in, void *out, int64_t count, cudaStream_t s);
-// dx = dy * gelu'(pre)
-void launch_gelu_backward(Dtype t, const void *pre, const void *dy, void *dx, int64_t count, cudaStream_t s);
 
 // ---- 256-way softmax cross-entropy (reference cuda/model.cuh:33-57) ----
 struct CrossEntropyArgs {
@@ -165,9 +162,22 @@ struct GemmArgs {
 void launch_gemm_simt(const GemmArgs &g, cudaStream_t s);
 // tcgen05 path; returns false when the shape/layout is outside what it supports.
 bool gemm_tc_supported(const GemmArgs &g);
-void launch_gemm_tc(const GemmArgs &g, int sms, StepCounters *counters, cudaStream_t s);
+// Split-K scratch of the tcgen05 GEMM: FP32 partial tiles, one ticket per output tile (zero between
+// launches) and a device error word.  An Engine owns one, so engines never share scratch; it is grown
+// by launch_gemm_tc when a schedule needs more (never during stream capture: the engine runs one eager
+// step first) and `generation` changes whenever a pointer does.
+struct GemmWorkspace {
+    float *partials = nullptr;
+    unsigned *tickets = nullptr;
+    StepCounters *error_word = nullptr;
+    size_t partial_bytes = 0, ticket_count = 0;
+    uint64_t generation = 1;
+};
+void release_gemm_workspace(GemmWorkspace &w);
+void launch_gemm_tc(const GemmArgs &g, int sms, StepCounters *counters, cudaStream_t s,
+                    GemmWorkspace *workspace = nullptr);
 int gemm_tc_shared_bytes();
-uint64_t gemm_tc_workspace_generation(); // bumped whenever the split-K workspace is reallocated
+int gemm_tc_take_device_error(cudaStream_t s);
 // Weight gradient dW[out, in] = dy^T x whose split-K scratch is a fixed array inside the library:
 // allocates nothing (see gemm_tc.cu).  Throws when the shape needs more scratch than the array holds.
 void launch_weight_gradient_static(const void *dy, const void *x, float *dw, int out, int in, int tokens, int sms,
@@ -220,6 +230,9 @@ struct MuonApplyArgs {
 };
 void launch_muon_apply(const MuonApplyArgs &a, cudaStream_t s);
 void launch_advance(StepCounters *counters, cudaStream_t s);
+
+// ---- self-test: a wait on a barrier nothing arms, with a short limit (selftest.cu) ----
+int launch_starved_wait(StepCounters *counters, double limit_ms, int code, cudaStream_t s);
 
 // ---- conversions ----
 void launch_split_weights(const float *w, bf16 *high, uint16_t *low, int64_t count, cudaStream_t s);

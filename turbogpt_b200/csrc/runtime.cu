@@ -184,6 +184,25 @@ int tg_ex_initialize_weights(const TgConfigEx *config, float *weights) {
         initialize_weights(*config, weights);
     });
 }
+uint64_t tg_ex_config_digest(const TgConfigEx *config) {
+    try {
+        validate_config(*config);
+    } catch (const std::exception &error) {
+        last_error = error.what();
+        return 0;
+    }
+    // Everything every rank of one job must agree on: all fields except the rank and the device.
+    TgConfigEx c = *config;
+    c.rank = 0, c.base.device = 0, c.base.reserved_ = 0;
+    uint64_t digest = 0x243f6a8885a308d3ull;
+    const unsigned char *bytes = reinterpret_cast<const unsigned char *>(&c);
+    for (size_t i = 0; i < sizeof(c); i += 8) {
+        uint64_t word = 0;
+        memcpy(&word, bytes + i, sizeof(c) - i < 8 ? sizeof(c) - i : 8);
+        digest = hash_u64(digest ^ word);
+    }
+    return digest ? digest : 1;
+}
 int tg_ex_nccl_unique_id(uint8_t *id128) {
     return guarded([&] {
         const Nccl &nccl = Nccl::get();
@@ -221,6 +240,24 @@ int tg_ex_profile(Engine *e, const char **names, double *milliseconds, int64_t *
     }
 }
 int64_t tg_ex_launch_count(Engine *e) { return e->launches; }
+int64_t tg_ex_read_activation(Engine *e, int layer, const char *name, float *out, int64_t capacity) {
+    try {
+        return e->read_activation(layer, name, out, capacity);
+    } catch (const std::exception &error) {
+        last_error = error.what();
+        return -1;
+    }
+}
+
+int tg_ex_selftest_bounded_wait(Engine *e, double limit_ms) {
+    try {
+        e->set_device();
+        return launch_starved_wait(e->counters, limit_ms, 901, e->stream);
+    } catch (const std::exception &error) {
+        last_error = error.what();
+        return -1;
+    }
+}
 
 static int device_sms() {
     int device = 0, sms = 0;
@@ -262,6 +299,15 @@ int tg_ex_weight_gradient_static(const void *dy, const void *x, float *dw, int o
             throw std::runtime_error("Missing weight-gradient operand");
         launch_weight_gradient_static(dy, x, dw, out, in, tokens, device_sms(), static_cast<cudaStream_t>(stream));
     });
+}
+int tg_ex_last_device_error(void *stream) {
+    try {
+        require_sm100();
+        return gemm_tc_take_device_error(static_cast<cudaStream_t>(stream));
+    } catch (const std::exception &error) {
+        last_error = error.what();
+        return -1;
+    }
 }
 int tg_ex_attention_forward(const void *qkv, void *out, float *lse, int batch, int context, int heads, int d_head,
                             int tensor_cores, void *stream) {

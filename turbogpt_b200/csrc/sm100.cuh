@@ -110,17 +110,20 @@ __device__ __forceinline__ bool mbarrier_try_wait(uint32_t bar, uint32_t parity)
 // returns false.  Callers leave their loops on false.
 constexpr unsigned long long WaitLimitNs = 2000000000ull;
 __device__ __forceinline__ bool mbarrier_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag,
-                                              StepCounters *counters, int code) {
+                                              StepCounters *counters, int code,
+                                              unsigned long long limit_ns = WaitLimitNs) {
     if (mbarrier_try_wait(bar, parity))
         return true;
     const unsigned long long start = global_timer();
+    // the clock is read every 256 polls (a poll may park the thread for up to 0.1 ms); short limits read it every poll
+    const unsigned stride_mask = limit_ns < 100000000ull ? 0u : 0xffu;
     for (unsigned spins = 1;; ++spins) {
         if (mbarrier_try_wait(bar, parity))
             return true;
-        if ((spins & 0xff) == 0) {
+        if ((spins & stride_mask) == 0) {
             if (*abort_flag)
                 return false;
-            if (global_timer() - start > WaitLimitNs) {
+            if (global_timer() - start > limit_ns) {
                 *abort_flag = 1;
                 if (counters)
                     atomicCAS(&counters->error, 0, code);
@@ -138,31 +141,6 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *map
                  "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y), "r"(z)
                  : "memory");
 }
-// 3-D tile store from shared memory; parts of the box outside the tensor are not written.
-// Contiguous global -> shared copy (16-byte aligned addresses, size a multiple of 16 bytes)
-// completing on an mbarrier.
-__device__ __forceinline__ void bulk_load(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
-                 "l"(src), "r"(bytes), "r"(bar)
-                 : "memory");
-}
-__device__ __forceinline__ void tma_store_3d(const CUtensorMap *map, uint32_t src, int x, int y, int z) {
-    asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(
-                     reinterpret_cast<uint64_t>(map)),
-                 "r"(src), "r"(x), "r"(y), "r"(z)
-                 : "memory");
-}
-__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
-// Waits until at most `pending` of this thread's store groups still read shared memory.
-__device__ __forceinline__ void bulk_wait_read(int pending) {
-    switch (pending) {
-    case 0: asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); break;
-    case 1: asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); break;
-    case 2: asm volatile("cp.async.bulk.wait_group.read 2;" ::: "memory"); break;
-    default: asm volatile("cp.async.bulk.wait_group.read 3;" ::: "memory"); break;
-    }
-}
-__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 __device__ __forceinline__ void prefetch_map(const CUtensorMap *map) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
 }
