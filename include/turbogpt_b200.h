@@ -125,6 +125,23 @@ int tg_ex_parameter_layout(const TgConfigEx *config, int64_t *offsets, int32_t *
                            int capacity);
 /* initialize_weights of model.cpp:7-31 for any architecture (same seeds per tensor role). */
 int tg_ex_initialize_weights(const TgConfigEx *config, float *weights);
+/* Training state as the reference's checkpoint.h:7-14 holds it, with caller-owned arrays. */
+typedef struct TgCheckpoint {
+    float *weights, *momentum, *variance; /* [tg_ex_parameter_count(config)] each */
+    double *final_loss_sums;              /* [config->base.context] */
+    uint64_t step, final_loss_batches;
+    double train_seconds;
+    TgOneCycle scheduler;
+} TgCheckpoint;
+/* save_training_state / load_training_state of checkpoint.cpp:506-579 for any architecture: the same
+ * torch.load-able archive with the same fifteen records the reference host reads by name, plus one
+ * record holding width, heads, hidden and the architecture selectors (checkpoint.cpp:164-166 stores
+ * depth and context only).  Files of the reference architecture load in the reference host; files
+ * the reference host wrote load here as the reference architecture.  Host-only: no device is touched.
+ * Loading fills the caller's arrays and fails with "Checkpoint architecture mismatch" when the file
+ * was written for other dimensions. */
+int tg_ex_save_checkpoint(const char *path, const TgConfigEx *config, const TgCheckpoint *state);
+int tg_ex_load_checkpoint(const char *path, const TgConfigEx *config, TgCheckpoint *state);
 /* A digest of everything the ranks of one data-parallel job must agree on (every field of *config
  * except rank and base.device; nccl_id included).  Ranks exchange it over their own channel and
  * refuse to call tg_create_ex when the values differ: a communicator created from mismatched
@@ -195,6 +212,18 @@ int tg_ex_attention_forward(const void *qkv, void *out, float *lse, int batch, i
 int tg_ex_attention_backward(const void *qkv, const void *out, const void *dout, const float *lse,
                              void *dqkv, int batch, int context, int heads, int d_head, int tensor_cores,
                              void *stream);
+/* RMSNorm (kind TG_NORM_RMS, eps 1e-6) or LayerNorm (TG_NORM_LAYER, eps 1e-5) over BF16 rows
+ * [rows, width] (cuda/ops.cuh:56-66).  Scale and bias are FP32 values passed as the engine stores
+ * them: the high 16 bits as BF16 (`*_high`) and the low 16 bits (`*_low`, uint16) in separate arrays;
+ * bias pointers are ignored for RMSNorm. */
+int tg_ex_norm_forward(int kind, const void *x, const void *scale_high, const void *scale_low, const void *bias_high,
+                       const void *bias_low, void *y, int rows, int width, void *stream);
+/* Its backward (cuda/ops.cuh:67-80): dx = norm'(dy) rounded to BF16, plus residual_in when not NULL
+ * (the running residual-stream gradient); dscale / dbias [width] FP32 are overwritten, summed over
+ * rows in a fixed order. */
+int tg_ex_norm_backward(int kind, const void *x, const void *dy, const void *scale_high, const void *scale_low,
+                        const void *residual_in, void *dx, float *dscale, float *dbias, int rows, int width,
+                        void *stream);
 /* 256-way softmax cross-entropy (cuda/model.cuh:33-57): losses[rows] floats, dlogits BF16
  * = (softmax - onehot) * scale, written in place over logits when dlogits == logits. */
 int tg_ex_cross_entropy(const void *logits, const uint8_t *targets, float *losses, void *dlogits, int rows,

@@ -119,3 +119,50 @@ def test_attention_matches_torch(batch, context, heads, d_head):
             lib.tg_error()
         torch.cuda.synchronize()
         assert max_relative(d_dqkv.float().cpu().numpy(), expected_dqkv) <= 1e-2, tensor_cores
+
+
+@pytest.mark.parametrize("rows,width", [(1000, 768), (515, 256), (300, 1024), (64, 96)])
+@pytest.mark.parametrize("kind", [0, 1])
+def test_norms_match_torch(rows, width, kind):
+    """RMSNorm / LayerNorm forward and backward (with the running residual gradient) as stand-alone
+    kernels against FP32 PyTorch: outputs within one BF16 rounding, scale and bias gradients (FP32,
+    fixed-order sums over rows) to 1e-4, and the same bits on a second call."""
+    from turbogpt_b200.microbench import split_fp32
+    lib = load_library()
+    g = torch.Generator().manual_seed(3)
+    x = (torch.randn(rows, width, generator=g) * 2 + .3).bfloat16()
+    dy = torch.randn(rows, width, generator=g).bfloat16()
+    residual = torch.randn(rows, width, generator=g).bfloat16()
+    scale = 1 + .2 * torch.randn(width, generator=g)
+    bias = .1 * torch.randn(width, generator=g)
+    xf = x.float().requires_grad_()
+    sf, bf = scale.clone().requires_grad_(), bias.clone().requires_grad_()
+    if kind == 1:
+        expected = torch.nn.functional.layer_norm(xf, (width,), sf, bf, eps=1e-5)
+    else:
+        expected = torch.nn.functional.rms_norm(xf, (width,), sf, eps=1e-6)
+    expected.backward(dy.float())
+    d_x, d_dy, d_res = x.cuda(), dy.cuda(), residual.cuda()
+    halves = [t.cuda() for t in (*split_fp32(scale), *split_fp32(bias))]
+    y = torch.zeros_like(d_x)
+    assert lib.tg_ex_norm_forward(kind, d_x.data_ptr(), halves[0].data_ptr(), halves[1].data_ptr(), halves[2].data_ptr(),
+                                  halves[3].data_ptr(), y.data_ptr(), rows, width, None) == 0, lib.tg_error()
+    torch.cuda.synchronize()
+    assert max_relative(y.float().cpu().numpy(), expected.detach().numpy()) <= 2.0 ** -8
+    results = []
+    for _ in range(2):
+        dx = torch.zeros_like(d_x)
+        dscale, dbias = torch.zeros(width, device="cuda"), torch.zeros(width, device="cuda")
+        assert lib.tg_ex_norm_backward(kind, d_x.data_ptr(), d_dy.data_ptr(), halves[0].data_ptr(), halves[1].data_ptr(),
+                                       d_res.data_ptr(), dx.data_ptr(), dscale.data_ptr(), dbias.data_ptr(), rows,
+                                       width, None) == 0, lib.tg_error()
+        torch.cuda.synchronize()
+        results.append((dx.float().cpu().numpy(), dscale.cpu().numpy(), dbias.cpu().numpy()))
+    dx, dscale, dbias = results[0]
+    expected_dx = residual.float() + xf.grad.bfloat16().float()  # rounded, then added to the residual gradient
+    assert max_relative(dx, expected_dx.numpy()) <= 2.0 ** -7
+    assert max_relative(dscale, sf.grad.numpy()) <= 1e-4
+    if kind == 1:
+        assert max_relative(dbias, bf.grad.numpy()) <= 1e-4
+    for a, b in zip(*results):
+        np.testing.assert_array_equal(a, b)

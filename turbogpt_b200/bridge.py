@@ -69,6 +69,13 @@ class OneCycle(C.Structure):
         super().__init__(total_steps, .3, .04, .000004, .85, .95)
 
 
+class Checkpoint(C.Structure):
+    """TgCheckpoint of include/turbogpt_b200.h: training state with caller-owned arrays."""
+    _fields_ = [('weights', C.c_void_p), ('momentum', C.c_void_p), ('variance', C.c_void_p),
+                ('final_loss_sums', C.c_void_p), ('step', C.c_uint64), ('final_loss_batches', C.c_uint64),
+                ('train_seconds', C.c_double), ('scheduler', OneCycle)]
+
+
 class StepRates(C.Structure):
     """optim.h:14-16."""
     _fields_ = [('multiplier', C.c_float), ('momentum', C.c_float)]
@@ -151,6 +158,8 @@ def load_library() -> C.CDLL:
     lib.tg_ex_parameter_count.restype = I64
     lib.tg_ex_parameter_layout.argtypes = [C.POINTER(ConfigEx), P, P, P, I]
     lib.tg_ex_initialize_weights.argtypes = [C.POINTER(ConfigEx), P]
+    lib.tg_ex_save_checkpoint.argtypes = [C.c_char_p, C.POINTER(ConfigEx), C.POINTER(Checkpoint)]
+    lib.tg_ex_load_checkpoint.argtypes = [C.c_char_p, C.POINTER(ConfigEx), C.POINTER(Checkpoint)]
     lib.tg_ex_config_digest.argtypes = [C.POINTER(ConfigEx)]
     lib.tg_ex_config_digest.restype = C.c_uint64
     lib.tg_ex_nccl_unique_id.argtypes = [P]
@@ -170,6 +179,8 @@ def load_library() -> C.CDLL:
     lib.tg_ex_last_device_error.argtypes = [P]
     lib.tg_ex_attention_forward.argtypes = [P, P, P, I, I, I, I, I, P]
     lib.tg_ex_attention_backward.argtypes = [P, P, P, P, P, I, I, I, I, I, P]
+    lib.tg_ex_norm_forward.argtypes = [I, P, P, P, P, P, P, I, I, P]
+    lib.tg_ex_norm_backward.argtypes = [I, P, P, P, P, P, P, P, P, I, I, P]
     lib.tg_ex_cross_entropy.argtypes = [P, P, P, P, I, C.c_float, P]
     _library = lib
     return lib
@@ -178,9 +189,9 @@ def load_library() -> C.CDLL:
 EXPORTS = ('error create destroy parameter_count blocks shared_bytes set_weights get_weights get_optimizer_state '
            'set_optimizer_state memory set_data train get_training_losses training_versions pipeline_stats '
            'onecycle_point set_onecycle batch predict optimizer_test synchronize').split()
-EXTENSIONS = ('reference_config gpt_config parameter_count parameter_layout initialize_weights config_digest nccl_unique_id '
+EXTENSIONS = ('reference_config gpt_config parameter_count parameter_layout initialize_weights config_digest save_checkpoint load_checkpoint nccl_unique_id '
               'stream sample train_mean_loss train_batch profile launch_count read_activation selftest_bounded_wait gemm weight_gradient_static last_device_error attention_forward attention_backward '
-              'cross_entropy').split()
+              'norm_forward norm_backward cross_entropy').split()
 
 
 class Native:
@@ -306,6 +317,38 @@ class Native:
         launches = (C.c_int64 * 32)()
         n = self.check(self.lib.tg_ex_profile(self.handle, names, ms, launches, 32, int(reset)))
         return {names[i].decode(): (ms[i], launches[i]) for i in range(n)}
+
+
+def save_checkpoint(path, config: ConfigEx, weights, momentum, variance, step, schedule: OneCycle,
+                    train_seconds=0.0, final_loss_sums=None, final_loss_batches=0) -> None:
+    """Writes the training state as a torch.load-able archive (the reference's checkpoint format plus
+    the model dimensions)."""
+    lib = load_library()
+    arrays = [np.ascontiguousarray(a, dtype=np.float32) for a in (weights, momentum, variance)]
+    sums = np.ascontiguousarray(final_loss_sums if final_loss_sums is not None else np.zeros(config.base.context),
+                                dtype=np.float64)
+    state = Checkpoint(arrays[0].ctypes.data, arrays[1].ctypes.data, arrays[2].ctypes.data, sums.ctypes.data, step,
+                       final_loss_batches, train_seconds, schedule)
+    if lib.tg_ex_save_checkpoint(str(path).encode(), C.byref(config), C.byref(state)) < 0:
+        raise RuntimeError(lib.tg_error().decode())
+
+
+def load_checkpoint(path, config: ConfigEx) -> dict:
+    lib = load_library()
+    count = lib.tg_ex_parameter_count(C.byref(config))
+    if count < 0:
+        raise RuntimeError(lib.tg_error().decode())
+    arrays = [np.empty(count, np.float32) for _ in range(3)]
+    sums = np.empty(config.base.context, np.float64)
+    state = Checkpoint(arrays[0].ctypes.data, arrays[1].ctypes.data, arrays[2].ctypes.data, sums.ctypes.data)
+    if lib.tg_ex_load_checkpoint(str(path).encode(), C.byref(config), C.byref(state)) < 0:
+        raise RuntimeError(lib.tg_error().decode())
+    schedule = OneCycle(state.scheduler.total_steps)
+    for name, _ in OneCycle._fields_:
+        setattr(schedule, name, getattr(state.scheduler, name))
+    return dict(weights=arrays[0], momentum=arrays[1], variance=arrays[2], step=int(state.step), schedule=schedule,
+                train_seconds=float(state.train_seconds), final_loss_sums=sums,
+                final_loss_batches=int(state.final_loss_batches))
 
 
 def require_matching_ranks(config: ConfigEx, all_gather) -> None:

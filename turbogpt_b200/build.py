@@ -10,7 +10,7 @@ from pathlib import Path
 PACKAGE = Path(__file__).resolve().parent
 CSRC = PACKAGE / "csrc"
 LIBRARY = PACKAGE / "libturbogpt_b200.so"
-SOURCES = ["host.cpp", "elementwise.cu", "attention_simt.cu", "gemm_simt.cu", "gemm_tc.cu", "attention_tc.cu", "optim.cu",
+SOURCES = ["host.cpp", "checkpoint.cpp", "elementwise.cu", "attention_simt.cu", "gemm_simt.cu", "gemm_tc.cu", "attention_tc.cu", "optim.cu",
            "selftest.cu", "engine.cu", "runtime.cu"]
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
          "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=default", "--expt-relaxed-constexpr"]
@@ -49,10 +49,12 @@ def build_library(verbose: bool = False, ptxas_info: bool = False) -> Path:
             if log:
                 print(log, file=sys.stderr)
     if _stale(LIBRARY, objects):
-        cmd = [nvcc, "-shared", "-o", str(LIBRARY), *objects, "-lcudart", "-ldl"]
+        staged = LIBRARY.with_name(LIBRARY.name + ".staged")  # linked aside, then moved into place in one step
+        cmd = [nvcc, "-shared", "-o", str(staged), *objects, "-lcudart", "-ldl"]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode:
             raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
+        os.replace(staged, LIBRARY)
     return LIBRARY
 
 

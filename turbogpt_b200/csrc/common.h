@@ -50,6 +50,8 @@ void validate_config(const TgConfigEx &c);           // throws std::runtime_erro
 Layout make_layout(const TgConfigEx &c);             // reference model.h:12-37 generalised
 void initialize_weights(const TgConfigEx &c, float *w); // reference model.cpp:7-31 generalised
 TgStepRates onecycle_point(const TgOneCycle &s, int step); // reference optim.h:18-44
+void save_checkpoint(const std::string &path, const TgConfigEx &c, const TgCheckpoint &s); // checkpoint.cpp
+void load_checkpoint(const std::string &path, const TgConfigEx &c, TgCheckpoint &s);
 
 static_assert(sizeof(TgConfig) == 72 && sizeof(TgOneCycle) == 48 && sizeof(TgStepRates) == 8,
               "struct layouts are part of the ABI (reference tests/bridge.py:7-26)");

@@ -256,39 +256,88 @@ __device__ __forceinline__ void unpack8(const Packet<float> &r, float (&v)[8]) {
 }
 
 // Widths of 256..1024 in steps of 256: the row lives in registers (one 128-bit load per 256
-// columns and lane), so x is read once; scale and bias are read once per thread.
-template <int V> __device__ __forceinline__ void row_moments(int kind, const float (&x)[V][8], int width,
-                                                            float &mean, float &inv) {
-    // four interleaved partial sums per quantity: the additions of a row are not one long chain
+// columns and lane), so x is read once; scale and bias are read once per block into shared memory.
+//
+// Per-lane vectors of 8 floats in shared memory are stored as two float4 planes,
+// [v][half][lane][4]: consecutive lanes then touch consecutive 16-byte words and a warp-wide access
+// has no bank conflicts (the natural [column] order puts lanes 32 bytes apart: two-way conflicts).
+__device__ __forceinline__ int plane_index(int v, int half, int lane) { return ((v * 2 + half) * 32 + lane) * 4; }
+__device__ __forceinline__ int plane_of_column(int c) { // column -> index in the plane layout
+    const int v = c / 256, lane = c % 256 / 8, half = c % 8 / 4, j = c % 4;
+    return plane_index(v, half, lane) + j;
+}
+__device__ __forceinline__ void load_planes(const float *base, int v, int lane, float (&w)[8]) {
+    const float4 a = *reinterpret_cast<const float4 *>(base + plane_index(v, 0, lane));
+    const float4 b = *reinterpret_cast<const float4 *>(base + plane_index(v, 1, lane));
+    w[0] = a.x, w[1] = a.y, w[2] = a.z, w[3] = a.w, w[4] = b.x, w[5] = b.y, w[6] = b.z, w[7] = b.w;
+}
+__device__ __forceinline__ void store_planes(float *base, int v, int lane, const float (&w)[8]) {
+    *reinterpret_cast<float4 *>(base + plane_index(v, 0, lane)) = make_float4(w[0], w[1], w[2], w[3]);
+    *reinterpret_cast<float4 *>(base + plane_index(v, 1, lane)) = make_float4(w[4], w[5], w[6], w[7]);
+}
+// Two sums over the warp at once: the shuffles of the two values interleave, so the pair costs the
+// latency of one reduction.
+__device__ __forceinline__ void warp_sum2(float &a, float &b) {
+#pragma unroll
+    for (int k = 16; k; k >>= 1) {
+        const float oa = __shfl_xor_sync(0xffffffffu, a, k), ob = __shfl_xor_sync(0xffffffffu, b, k);
+        a += oa, b += ob;
+    }
+}
+// Mean and 1/sqrt(variance + eps) of a register-resident row.  FP32 rows (the check mode) take two
+// passes like the FP32 model they are compared with; BF16 rows take one pass over values shifted by
+// the row's first element (exact for the shift, immune to a large common offset), whose two sums
+// share one warp reduction: the row's dependent chain is one shuffle plus one reduction.
+template <class T, int V> __device__ __forceinline__ void row_moments(int kind, const float (&x)[V][8], int width,
+                                                                       float &mean, float &inv) {
     float sums[4] = {0, 0, 0, 0}, squares[4] = {0, 0, 0, 0};
-#pragma unroll
-    for (int v = 0; v < V; ++v)
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            sums[j % 4] += x[v][j];
-            squares[j % 4] += x[v][j] * x[v][j];
-        }
     if (kind == TG_NORM_RMS) {
+#pragma unroll
+        for (int v = 0; v < V; ++v)
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                squares[j % 4] += x[v][j] * x[v][j];
         mean = 0;
         inv = rsqrtf(warp_sum((squares[0] + squares[1]) + (squares[2] + squares[3])) / width + 1e-6f);
         return;
     }
-    mean = warp_sum((sums[0] + sums[1]) + (sums[2] + sums[3])) / width;
-    float centred[4] = {0, 0, 0, 0};
+    if constexpr (sizeof(T) == 4) {
 #pragma unroll
-    for (int v = 0; v < V; ++v)
+        for (int v = 0; v < V; ++v)
 #pragma unroll
-        for (int j = 0; j < 8; ++j)
-            centred[j % 4] += (x[v][j] - mean) * (x[v][j] - mean);
-    inv = rsqrtf(warp_sum((centred[0] + centred[1]) + (centred[2] + centred[3])) / width + 1e-5f);
+            for (int j = 0; j < 8; ++j)
+                sums[j % 4] += x[v][j];
+        mean = warp_sum((sums[0] + sums[1]) + (sums[2] + sums[3])) / width;
+#pragma unroll
+        for (int v = 0; v < V; ++v)
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                squares[j % 4] += (x[v][j] - mean) * (x[v][j] - mean);
+        inv = rsqrtf(warp_sum((squares[0] + squares[1]) + (squares[2] + squares[3])) / width + 1e-5f);
+    } else {
+        const float shift = __shfl_sync(0xffffffffu, x[0][0], 0);
+#pragma unroll
+        for (int v = 0; v < V; ++v)
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const float d = x[v][j] - shift;
+                sums[j % 4] += d;
+                squares[j % 4] += d * d;
+            }
+        float s1 = (sums[0] + sums[1]) + (sums[2] + sums[3]), s2 = (squares[0] + squares[1]) + (squares[2] + squares[3]);
+        warp_sum2(s1, s2);
+        const float offset = s1 / width;
+        mean = shift + offset;
+        inv = rsqrtf(fmaxf(s2 / width - offset * offset, 0.f) + 1e-5f);
+    }
 }
 template <class T, int V> __global__ void __launch_bounds__(256, 4) norm_rows_kernel(NormArgs a) {
     sm100::grid_launch_dependents(); // the next kernel may set itself up while this one runs
-    __shared__ __align__(16) float sw[V * 256], sb[V * 256]; // FP32 scale and bias, shared by the block's rows
+    __shared__ __align__(16) float sw[V * 256], sb[V * 256]; // FP32 scale and bias in the plane layout
     const int lane = threadIdx.x % 32, warps = blockDim.x / 32;
     for (int c = threadIdx.x; c < V * 256; c += blockDim.x) {
-        sw[c] = join_weight(a.scale_high[c], a.scale_low[c]);
-        sb[c] = a.kind == TG_NORM_LAYER ? join_weight(a.bias_high[c], a.bias_low[c]) : 0.f;
+        sw[plane_of_column(c)] = join_weight(a.scale_high[c], a.scale_low[c]);
+        sb[plane_of_column(c)] = a.kind == TG_NORM_LAYER ? join_weight(a.bias_high[c], a.bias_low[c]) : 0.f;
     }
     __syncthreads();
     const int stride = gridDim.x * warps;
@@ -309,12 +358,14 @@ template <class T, int V> __global__ void __launch_bounds__(256, 4) norm_rows_ke
             for (int k = 0; k < V; ++k)
                 fetch8((const T *)a.x + int64_t(row + stride) * a.width + (k * 32 + lane) * 8, next[k]);
         float mean, inv;
-        row_moments<V>(a.kind, v, a.width, mean, inv);
+        row_moments<T, V>(a.kind, v, a.width, mean, inv);
+        if (a.stats && lane == 0)
+            reinterpret_cast<float2 *>(a.stats)[row] = make_float2(mean, inv); // kept for the backward pass
 #pragma unroll
         for (int k = 0; k < V; ++k) {
             float out[8], w[8], b[8];
-            load8(sw + (k * 32 + lane) * 8, w);
-            load8(sb + (k * 32 + lane) * 8, b);
+            load_planes(sw, k, lane, w);
+            load_planes(sb, k, lane, b);
 #pragma unroll
             for (int j = 0; j < 8; ++j)
                 out[j] = a.kind == TG_NORM_RMS ? v[k][j] * inv * w[j] : (v[k][j] - mean) * inv * w[j] + b[j];
@@ -426,24 +477,29 @@ __global__ void __launch_bounds__(256) norm_backward_reduce_kernel(const float *
     }
 }
 // Register-resident variant for widths 256..1024: x, dy and the residual gradient are read once, and
-// a warp fetches its next row while it works on the current one.  Each warp keeps the scale/bias
-// gradient sums of its rows in its own slice of shared memory (a lane owns its columns there);
-// warps are summed in order at the end, blocks in order by the reduce kernel: deterministic.
+// a warp fetches its next row while it works on the current one.  The row's mean and 1/sigma come
+// from the forward pass when it saved them (`stats`), so the only reduction a row waits for is the
+// pair sum(dz), sum(dz z).  Each warp keeps the scale/bias gradient sums of its rows in its own slice
+// of shared memory (plane layout: a lane owns its words, no conflicts, no atomics); warps are summed
+// in order at the end, blocks in order by the reduce kernel: deterministic.
 template <class T, int V> __global__ void __launch_bounds__(256, 2) norm_backward_rows_kernel(NormBackwardArgs a) {
     sm100::grid_launch_dependents(); // the next kernel may set itself up while this one runs
-    extern __shared__ float sums[]; // [V * 256] scale, then [warps][2][V * 256] gradient sums
+    extern __shared__ float sums[]; // [V * 256] scale, then [warps][2][V * 256] gradient sums, all in the plane layout
     const int lane = threadIdx.x % 32, warp = threadIdx.x / 32, warps = blockDim.x / 32;
     float *scale = sums, *mine = sums + V * 256 + warp * 2 * V * 256;
     for (int c = threadIdx.x; c < V * 256; c += blockDim.x)
-        scale[c] = join_weight(a.scale_high[c], a.scale_low[c]);
+        scale[plane_of_column(c)] = join_weight(a.scale_high[c], a.scale_low[c]);
     for (int c = lane; c < 2 * V * 256; c += 32)
         mine[c] = 0.f;
     __syncthreads();
-    const bool residual = a.residual_in != nullptr;
+    const bool residual = a.residual_in != nullptr, saved = a.stats != nullptr;
     const int stride = gridDim.x * warps;
     Packet<T> nx[V], ng[V], nr[V];
+    float2 nstat = make_float2(0.f, 1.f);
     auto fetch = [&](int row) {
         const int64_t offset = int64_t(row) * a.width;
+        if (saved)
+            nstat = reinterpret_cast<const float2 *>(a.stats)[row];
 #pragma unroll
         for (int v = 0; v < V; ++v) {
             fetch8((const T *)a.x + offset + (v * 32 + lane) * 8, nx[v]);
@@ -465,18 +521,18 @@ template <class T, int V> __global__ void __launch_bounds__(256, 2) norm_backwar
             unpack8(ng[v], g[v]);
             r[v] = nr[v];
         }
+        float mean = nstat.x, inv = nstat.y;
         if (row + stride < a.rows)
             fetch(row + stride); // in flight during this row's arithmetic
-        float mean, inv;
-        row_moments<V>(a.kind, x, a.width, mean, inv);
+        if (!saved)
+            row_moments<T, V>(a.kind, x, a.width, mean, inv);
         float part_dz[4] = {0, 0, 0, 0}, part_dzz[4] = {0, 0, 0, 0};
 #pragma unroll
         for (int v = 0; v < V; ++v) {
             float w[8], dw[8], db[8];
-            float *slot = mine + (v * 32 + lane) * 8;
-            load8(scale + (v * 32 + lane) * 8, w);
-            load8(slot, dw);
-            load8(slot + V * 256, db);
+            load_planes(scale, v, lane, w);
+            load_planes(mine, v, lane, dw);
+            load_planes(mine + V * 256, v, lane, db);
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
                 const float z = (x[v][j] - mean) * inv, dz = g[v][j] * w[j];
@@ -487,12 +543,14 @@ template <class T, int V> __global__ void __launch_bounds__(256, 2) norm_backwar
                 db[j] += g[v][j];
                 g[v][j] = dz; // keep dy * scale
             }
-            store8(slot, dw);
-            store8(slot + V * 256, db);
+            store_planes(mine, v, lane, dw);
+            store_planes(mine + V * 256, v, lane, db);
         }
-        const float sum_dzz = warp_sum((part_dzz[0] + part_dzz[1]) + (part_dzz[2] + part_dzz[3])) / a.width;
-        const float sum_dz =
-            a.kind == TG_NORM_LAYER ? warp_sum((part_dz[0] + part_dz[1]) + (part_dz[2] + part_dz[3])) / a.width : 0.f;
+        float sum_dzz = (part_dzz[0] + part_dzz[1]) + (part_dzz[2] + part_dzz[3]);
+        float sum_dz = (part_dz[0] + part_dz[1]) + (part_dz[2] + part_dz[3]);
+        warp_sum2(sum_dzz, sum_dz);
+        sum_dzz /= a.width;
+        sum_dz = a.kind == TG_NORM_LAYER ? sum_dz / a.width : 0.f;
 #pragma unroll
         for (int v = 0; v < V; ++v) {
             float out[8];
@@ -511,9 +569,10 @@ template <class T, int V> __global__ void __launch_bounds__(256, 2) norm_backwar
     }
     __syncthreads();
     for (int c = threadIdx.x; c < 2 * a.width; c += blockDim.x) {
+        const int which = c / a.width, index = plane_of_column(c % a.width) + which * V * 256;
         float total = 0;
         for (int k = 0; k < warps; ++k)
-            total += sums[V * 256 + k * 2 * a.width + c];
+            total += sums[V * 256 + k * 2 * V * 256 + index];
         a.partial[int64_t(blockIdx.x) * 2 * a.width + c] = total;
     }
 }

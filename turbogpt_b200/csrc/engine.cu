@@ -30,10 +30,13 @@ const Nccl &Nccl::get() {
         } else {
             api.GetUniqueId = reinterpret_cast<decltype(api.GetUniqueId)>(dlsym(lib, "ncclGetUniqueId"));
             api.CommInitRank = reinterpret_cast<decltype(api.CommInitRank)>(dlsym(lib, "ncclCommInitRank"));
+            api.CommInitRankConfig =
+                reinterpret_cast<decltype(api.CommInitRankConfig)>(dlsym(lib, "ncclCommInitRankConfig"));
             api.AllReduce = reinterpret_cast<decltype(api.AllReduce)>(dlsym(lib, "ncclAllReduce"));
+            api.AllGather = reinterpret_cast<decltype(api.AllGather)>(dlsym(lib, "ncclAllGather"));
             api.CommDestroy = reinterpret_cast<decltype(api.CommDestroy)>(dlsym(lib, "ncclCommDestroy"));
             api.GetErrorString = reinterpret_cast<decltype(api.GetErrorString)>(dlsym(lib, "ncclGetErrorString"));
-            if (!api.GetUniqueId || !api.CommInitRank || !api.AllReduce || !api.CommDestroy)
+            if (!api.GetUniqueId || !api.CommInitRank || !api.AllReduce || !api.AllGather || !api.CommDestroy)
                 failure = "NCCL library lacks a required symbol";
             else
                 loaded = true;
@@ -48,6 +51,8 @@ void Nccl::check(int result, const char *what) const {
         throw std::runtime_error(std::string(what) + ": " +
                                  (GetErrorString ? GetErrorString(result) : "NCCL error"));
 }
+
+constexpr int ExchangeSms = 4; // CTAs of the gradient all-reduce = SMs the backward GEMMs leave free for it
 
 // ------------------------------------------------------------------------------- setup -------
 template <class T> void Engine::allocate(T *&p, size_t n, bool zero) {
@@ -92,6 +97,7 @@ void Engine::initialize() {
     tensor_cores = !(c.flags & TG_FLAG_NO_TENSOR_CORES);
     profile = c.flags & TG_FLAG_PROFILE;
     tokens = c.base.batch * c.base.context;
+    gemm_sms = sms;
     CHECK_CUDA(cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking));
 
     const int64_t P = layout.count;
@@ -129,6 +135,8 @@ void Engine::initialize() {
         bytes(a.wide, M * wide);
         bytes(a.activated, M * Hd);
         a.selected = nullptr, a.gates = a.derivatives = a.lse = nullptr;
+        allocate(a.stats1, M * 2, false);
+        allocate(a.stats2, M * 2, false);
         if (c.attention == TG_ATTENTION_ARGMAX) {
             allocate(a.selected, M * c.heads, false);
             allocate(a.gates, M * c.heads, false);
@@ -139,6 +147,7 @@ void Engine::initialize() {
     }
     bytes(final_x, M * W);
     bytes(final_normed, M * W);
+    allocate(final_stats, M * 2, false);
     bytes(logits, M * Vocabulary);
     bytes(dhidden[0], M * W);
     bytes(dhidden[1], M * W);
@@ -185,7 +194,20 @@ void Engine::initialize() {
         const Nccl &nccl = Nccl::get();
         Nccl::UniqueId id;
         memcpy(id.internal, c.nccl_id, sizeof(id.internal));
-        nccl.check(nccl.CommInitRank(&comm, c.world, id, c.rank), "ncclCommInitRank");
+        // The GEMM kernel is one persistent CTA per SM holding all of its shared memory, so a collective
+        // kernel cannot share an SM with it: it either waits for a GEMM to end or takes SMs the next GEMM
+        // then waits for, with its tiles statically assigned.  The exchange needs little bandwidth
+        // (one layer's gradients per ~1.5 ms of backward), so the communicator is limited to
+        // ExchangeSms CTAs and the backward GEMMs leave that many SMs free (Engine::gemm_sms).
+        if (nccl.CommInitRankConfig) {
+            Nccl::Config limits{};
+            limits.size = sizeof(limits), limits.magic = 0xcafebeefu, limits.version = 21700;
+            limits.blocking = 1, limits.cga_cluster_size = INT32_MIN, limits.min_ctas = 1, limits.max_ctas = ExchangeSms;
+            limits.net_name = nullptr;
+            nccl.check(nccl.CommInitRankConfig(&comm, c.world, id, c.rank, &limits), "ncclCommInitRankConfig");
+        } else {
+            nccl.check(nccl.CommInitRank(&comm, c.world, id, c.rank), "ncclCommInitRank");
+        }
         int least, greatest;
         CHECK_CUDA(cudaDeviceGetStreamPriorityRange(&least, &greatest));
         CHECK_CUDA(cudaStreamCreateWithPriority(&exchange_stream, cudaStreamNonBlocking, greatest));
@@ -270,7 +292,7 @@ void Engine::gemm(Family f, GemmArgs g) {
     g.in = act;
     run(f, [&] {
         if (tensor_cores && gemm_tc_supported(g))
-            launch_gemm_tc(g, sms, counters, stream, &gemm_workspace);
+            launch_gemm_tc(g, gemm_sms, counters, stream, &gemm_workspace);
         else
             launch_gemm_simt(g, stream);
     });
@@ -341,9 +363,9 @@ void Engine::forward(bool want_gradient, bool dump_logits) {
     const int W = c.width, Hd = c.hidden, H = c.heads;
     const int depth = c.base.depth;
     const bool layer_norm = c.norm == TG_NORM_LAYER;
-    auto norm = [&](const void *in, int64_t scale, int64_t bias, void *out) {
+    auto norm = [&](const void *in, int64_t scale, int64_t bias, void *out, float *stats) {
         NormArgs a{c.norm, in, weight_high + scale, layer_norm ? weight_high + bias : nullptr, weight_low + scale,
-                   layer_norm ? weight_low + bias : nullptr, out, M, W};
+                   layer_norm ? weight_low + bias : nullptr, out, M, W, stats};
         run(FNorm, [&] { launch_norm(act, a, stream); });
     };
     run(FEmbedding, [&] { launch_embedding(act, weight(layout.embedding), x, layers[0].x, M, W, stream); });
@@ -351,7 +373,7 @@ void Engine::forward(bool want_gradient, bool dump_logits) {
         LayerActivations &a = layers[l];
         const LayerOffsets &p = layout.layers[l];
         void *next = l + 1 < depth ? layers[l + 1].x : final_x;
-        norm(a.x, p.attention_norm, p.attention_norm_bias, a.normed1);
+        norm(a.x, p.attention_norm, p.attention_norm_bias, a.normed1, a.stats1);
         GemmArgs qkv;
         qkv.a = a.normed1, qkv.a_row = W, qkv.b = weight(p.qkv), qkv.b_row = W, qkv.c = a.qkv, qkv.ldc = 3 * W;
         qkv.m = M, qkv.n = 3 * W, qkv.k = W, qkv.out = act;
@@ -375,7 +397,7 @@ void Engine::forward(bool want_gradient, bool dump_logits) {
         proj.ldc = W, proj.m = M, proj.n = W, proj.k = W, proj.out = act;
         proj.epilogue = Epilogue::Residual, proj.r = a.x, proj.ldr = W;
         gemm(FGemmForward, proj);
-        norm(a.middle, p.mlp_norm, p.mlp_norm_bias, a.normed2);
+        norm(a.middle, p.mlp_norm, p.mlp_norm_bias, a.normed2, a.stats2);
         GemmArgs up;
         up.a = a.normed2, up.a_row = W, up.b = weight(p.gate), up.b_row = W, up.c = a.wide, up.m = M, up.k = W;
         up.out = act;
@@ -393,7 +415,7 @@ void Engine::forward(bool want_gradient, bool dump_logits) {
         down.epilogue = Epilogue::Residual, down.r = a.middle, down.ldr = W;
         gemm(FGemmForward, down);
     }
-    norm(final_x, layout.final_norm, layout.final_norm_bias, final_normed);
+    norm(final_x, layout.final_norm, layout.final_norm_bias, final_normed, final_stats);
     GemmArgs head;
     head.a = final_normed, head.a_row = W, head.b = weight(layout.head), head.b_row = W, head.c = logits;
     head.ldc = Vocabulary, head.m = M, head.n = Vocabulary, head.k = W, head.out = act;
@@ -451,16 +473,25 @@ void Engine::backward() {
         return g;
     };
     auto norm_back = [&](const void *xin, const void *dy, int64_t scale, int64_t bias, const void *residual,
-                         void *dx) {
+                         void *dx, const float *stats) {
         NormBackwardArgs a{c.norm, xin, dy, weight_high + scale, weight_low + scale, residual, dx, norm_partial,
-                           gradient + scale, layer_norm ? gradient + bias : nullptr, M, W, norm_blocks};
+                           gradient + scale, layer_norm ? gradient + bias : nullptr, M, W, norm_blocks, stats};
         run(FNormBackward, [&] { launch_norm_backward(act, a, stream); });
     };
     void *dh = dhidden[0], *dh_other = dhidden[1];
+    // From the first bucket to the end of backward a collective may be running beside the GEMMs.
+    struct Reserve {
+        Engine &e;
+        explicit Reserve(Engine &engine) : e(engine) {
+            if (e.comm && e.sms > 4 * ExchangeSms)
+                e.gemm_sms = (e.sms - ExchangeSms) & ~1;
+        }
+        ~Reserve() { e.gemm_sms = e.sms; }
+    } reserve(*this);
 
     weight_grad(logits, Vocabulary, final_normed, W, layout.head);
     gemm(FGemmInputGrad, input_grad(logits, Vocabulary, layout.head, W, dbranch));
-    norm_back(final_x, dbranch, layout.final_norm, layout.final_norm_bias, nullptr, dh);
+    norm_back(final_x, dbranch, layout.final_norm, layout.final_norm_bias, nullptr, dh, final_stats);
     if (!c.tied) // final norm + head form the first bucket; a tied head waits for the embedding scatter
         exchange_bucket(layout.final_norm, layout.count, depth);
     else
@@ -480,7 +511,7 @@ void Engine::backward() {
         }
         weight_grad(dwide, wide, a.normed2, W, p.gate);
         gemm(FGemmInputGrad, input_grad(dwide, wide, p.gate, W, dbranch));
-        norm_back(a.middle, dbranch, p.mlp_norm, p.mlp_norm_bias, dh, dh_other);
+        norm_back(a.middle, dbranch, p.mlp_norm, p.mlp_norm_bias, dh, dh_other, a.stats2);
         std::swap(dh, dh_other);
 
         weight_grad(dh, W, a.attended, W, p.attention);
@@ -504,7 +535,7 @@ void Engine::backward() {
             run(FMisc, [&] { launch_rope(act, dqkv, M, T, W, H, true, stream); });
         weight_grad(dqkv, 3 * W, a.normed1, W, p.qkv);
         gemm(FGemmInputGrad, input_grad(dqkv, 3 * W, p.qkv, W, dbranch));
-        norm_back(a.x, dbranch, p.attention_norm, p.attention_norm_bias, dh, dh_other);
+        norm_back(a.x, dbranch, p.attention_norm, p.attention_norm_bias, dh, dh_other, a.stats1);
         std::swap(dh, dh_other);
         int64_t layer_end = l + 1 < depth ? layout.layers[l + 1].attention_norm : layout.final_norm;
         exchange_bucket(p.attention_norm, layer_end, l);
@@ -524,23 +555,31 @@ void Engine::muon_family(int64_t first_offset, int rows, int cols) {
     const int64_t stride = depth > 1 ? layout.layers[1].qkv - layout.layers[0].qkv : 0;
     const int r = std::min(rows, cols), n = std::max(rows, cols); // orthogonalise the wide orientation
     const int64_t per = int64_t(rows) * cols;
+    // Under data parallelism the gradients are identical on every rank after the exchange, so the
+    // Newton-Schulz iterations (the expensive part: 15 GEMMs per family) are sharded by layer: rank k
+    // orthogonalises layers k*depth/world .. (k+1)*depth/world-1 and the BF16 results are
+    // all-gathered; momentum and the weight update run for every layer on every rank, so replicas
+    // stay bit-identical and any rank can write a checkpoint.
+    const bool sharded = comm && depth % c.world == 0 && depth >= c.world;
+    const int mine = sharded ? depth / c.world : depth, first = sharded ? c.rank * mine : 0;
     MuonPrepareArgs prep{gradient + first_offset, momentum + first_offset, muon_x[0], muon_sumsq, sumsq_partial,
                          sumsq_blocks, schedule, counters, c.base.momentum, c.base.clip, rows, cols, depth, stride};
     run(FMuon, [&] { launch_muon_prepare(prep, stream); });
     run(FMuon, [&] { launch_muon_normalize(muon_x[0], muon_sumsq, per, depth, stream); });
-    bf16 *cur = muon_x[0], *nxt = muon_x[1];
+    bf16 *cur = muon_x[0] + first * per, *nxt = muon_x[1] + first * per;
+    bf16 *a_buffer = muon_a + int64_t(first) * r * r, *b_buffer = muon_b + int64_t(first) * r * r;
     for (int it = 0; it < c.base.ns_steps; ++it) {
         GemmArgs a; // A = X X^T
-        a.a = cur, a.a_row = n, a.b = cur, a.b_row = n, a.c = muon_a, a.ldc = r, a.m = r, a.n = r, a.k = n;
-        a.batch = depth, a.a_batch = per, a.b_batch = per, a.c_batch = int64_t(r) * r, a.out = Dtype::BF16;
+        a.a = cur, a.a_row = n, a.b = cur, a.b_row = n, a.c = a_buffer, a.ldc = r, a.m = r, a.n = r, a.k = n;
+        a.batch = mine, a.a_batch = per, a.b_batch = per, a.c_batch = int64_t(r) * r, a.out = Dtype::BF16;
         GemmArgs b; // B = -4.775 A + 2.0315 A A
-        b.a = muon_a, b.a_row = r, b.b = muon_a, b.b_row = 1, b.b_col = r, b.c = muon_b, b.ldc = r;
-        b.m = r, b.n = r, b.k = r, b.batch = depth, b.a_batch = b.b_batch = b.c_batch = b.r_batch = int64_t(r) * r;
-        b.epilogue = Epilogue::Axpby, b.alpha = 2.0315f, b.beta = -4.775f, b.r = muon_a, b.ldr = r;
+        b.a = a_buffer, b.a_row = r, b.b = a_buffer, b.b_row = 1, b.b_col = r, b.c = b_buffer, b.ldc = r;
+        b.m = r, b.n = r, b.k = r, b.batch = mine, b.a_batch = b.b_batch = b.c_batch = b.r_batch = int64_t(r) * r;
+        b.epilogue = Epilogue::Axpby, b.alpha = 2.0315f, b.beta = -4.775f, b.r = a_buffer, b.ldr = r;
         b.out = Dtype::BF16;
         GemmArgs x2; // X' = 3.4445 X + B X
-        x2.a = muon_b, x2.a_row = r, x2.b = cur, x2.b_row = 1, x2.b_col = n, x2.c = nxt, x2.ldc = n;
-        x2.m = r, x2.n = n, x2.k = r, x2.batch = depth, x2.a_batch = int64_t(r) * r;
+        x2.a = b_buffer, x2.a_row = r, x2.b = cur, x2.b_row = 1, x2.b_col = n, x2.c = nxt, x2.ldc = n;
+        x2.m = r, x2.n = n, x2.k = r, x2.batch = mine, x2.a_batch = int64_t(r) * r;
         x2.b_batch = x2.c_batch = x2.r_batch = per;
         x2.epilogue = Epilogue::Axpby, x2.alpha = 1.f, x2.beta = 3.4445f, x2.r = cur, x2.ldr = n;
         x2.out = Dtype::BF16;
@@ -555,7 +594,14 @@ void Engine::muon_family(int64_t first_offset, int rows, int cols) {
         }
         std::swap(cur, nxt);
     }
-    MuonApplyArgs apply{cur, weight_high + first_offset, weight_low + first_offset,
+    bf16 *all = cur - first * per; // the buffer holding every layer's result
+    if (sharded) {
+        const Nccl &nccl = Nccl::get();
+        run(FExchange, [&] {
+            nccl.check(nccl.AllGather(cur, all, size_t(mine) * per, Nccl::Bfloat16, comm, stream), "ncclAllGather");
+        });
+    }
+    MuonApplyArgs apply{all, weight_high + first_offset, weight_low + first_offset,
                         weight_fp32 ? weight_fp32 + first_offset : nullptr, schedule, counters, c.base.muon_lr,
                         c.base.weight_decay, rows, cols, depth, stride};
     run(FMuon, [&] { launch_muon_apply(apply, stream); });

@@ -14,7 +14,17 @@ struct Nccl {
     };
     int (*GetUniqueId)(UniqueId *) = nullptr;
     int (*CommInitRank)(Comm *, int, UniqueId, int) = nullptr;
+    // ncclConfig_t as NCCL 2.17 laid it out; later libraries read `size` and `version` and fill the
+    // fields added since with their defaults.
+    struct Config {
+        size_t size;
+        unsigned magic, version;
+        int blocking, cga_cluster_size, min_ctas, max_ctas;
+        const char *net_name;
+    };
+    int (*CommInitRankConfig)(Comm *, int, UniqueId, int, Config *) = nullptr; // optional (NCCL >= 2.17)
     int (*AllReduce)(const void *, void *, size_t, int, int, Comm, cudaStream_t) = nullptr;
+    int (*AllGather)(const void *, void *, size_t, int, Comm, cudaStream_t) = nullptr;
     int (*CommDestroy)(Comm) = nullptr;
     const char *(*GetErrorString)(int) = nullptr;
     static const Nccl &get(); // throws when NCCL cannot be loaded
@@ -33,6 +43,7 @@ struct LayerActivations { // saved by forward for backward (reference cuda/types
     void *x, *normed1, *qkv, *attended, *middle, *normed2, *wide, *activated; // wide: gate|up, or gelu'(pre-activation)
     int *selected;
     float *gates, *derivatives, *lse;
+    float *stats1, *stats2; // per row: mean and 1/sigma of the two norms, saved by forward for backward
 };
 
 enum class RunMode { Evaluate, Gradients, Train, OptimizerOnly }; // reference cuda/trainer.cuh:6
@@ -59,6 +70,7 @@ struct Engine {
     // activations
     std::vector<LayerActivations> layers;
     void *final_x = nullptr, *final_normed = nullptr, *logits = nullptr;
+    float *final_stats = nullptr;
     void *dhidden[2] = {nullptr, nullptr}, *dbranch = nullptr, *dwide = nullptr, *dactivated = nullptr,
          *dqkv = nullptr;
     float *attention_scratch = nullptr; // dt (arg-max) or delta (softmax)
@@ -77,6 +89,7 @@ struct Engine {
     bool losses_reduced = true;
     // data parallel
     Nccl::Comm comm = nullptr;
+    int gemm_sms = 0; // SMs the GEMMs of the current phase may use (fewer while a gradient bucket may be in flight)
     std::vector<cudaEvent_t> bucket_events;
     cudaEvent_t exchange_done = nullptr;
     // profiling

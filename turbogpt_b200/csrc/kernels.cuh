@@ -44,6 +44,7 @@ struct NormArgs {
     const uint16_t *scale_low, *bias_low; // bias pointers are nullptr for RMSNorm
     void *y;
     int rows, width;
+    float *stats = nullptr; // optional [rows][2]: mean and 1/sqrt(variance + eps) of every row, for the backward pass
 };
 void launch_norm(Dtype t, const NormArgs &a, cudaStream_t s);
 struct NormBackwardArgs {
@@ -56,6 +57,7 @@ struct NormBackwardArgs {
     float *partial;          // [blocks][2][width] scratch for scale/bias gradients
     float *dscale, *dbias;   // outputs (overwritten); dbias nullptr for RMSNorm
     int rows, width, blocks;
+    const float *stats = nullptr; // [rows][2] from the forward pass (nullptr: recomputed from x)
 };
 void launch_norm_backward(Dtype t, const NormBackwardArgs &a, cudaStream_t s);
 int norm_backward_blocks(int rows, int sms);

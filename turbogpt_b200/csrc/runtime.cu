@@ -184,6 +184,20 @@ int tg_ex_initialize_weights(const TgConfigEx *config, float *weights) {
         initialize_weights(*config, weights);
     });
 }
+int tg_ex_save_checkpoint(const char *path, const TgConfigEx *config, const TgCheckpoint *state) {
+    return guarded([&] {
+        if (!path || !config || !state)
+            throw std::runtime_error("Missing checkpoint argument");
+        save_checkpoint(path, *config, *state);
+    });
+}
+int tg_ex_load_checkpoint(const char *path, const TgConfigEx *config, TgCheckpoint *state) {
+    return guarded([&] {
+        if (!path || !config || !state)
+            throw std::runtime_error("Missing checkpoint argument");
+        load_checkpoint(path, *config, *state);
+    });
+}
 uint64_t tg_ex_config_digest(const TgConfigEx *config) {
     try {
         validate_config(*config);
@@ -342,6 +356,42 @@ int tg_ex_attention_backward(const void *qkv, const void *out, const void *dout,
             launch_softmax_attention_backward(Dtype::BF16, a, static_cast<cudaStream_t>(stream));
         }
         CHECK_CUDA(cudaFreeAsync(delta, static_cast<cudaStream_t>(stream)));
+        CHECK_CUDA(cudaGetLastError());
+    });
+}
+int tg_ex_norm_forward(int kind, const void *x, const void *scale_high, const void *scale_low, const void *bias_high,
+                       const void *bias_low, void *y, int rows, int width, void *stream) {
+    return guarded([&] {
+        require_sm100();
+        if (!x || !y || !scale_high || !scale_low || (kind == TG_NORM_LAYER && (!bias_high || !bias_low)))
+            throw std::runtime_error("Missing norm operand");
+        if (width < 8 || width % 8 || rows < 1)
+            throw std::runtime_error("norm: width must be a positive multiple of 8");
+        NormArgs a{kind, x, static_cast<const bf16 *>(scale_high),
+                   kind == TG_NORM_LAYER ? static_cast<const bf16 *>(bias_high) : nullptr,
+                   static_cast<const uint16_t *>(scale_low),
+                   kind == TG_NORM_LAYER ? static_cast<const uint16_t *>(bias_low) : nullptr, y, rows, width};
+        launch_norm(Dtype::BF16, a, static_cast<cudaStream_t>(stream));
+        CHECK_CUDA(cudaGetLastError());
+    });
+}
+int tg_ex_norm_backward(int kind, const void *x, const void *dy, const void *scale_high, const void *scale_low,
+                        const void *residual_in, void *dx, float *dscale, float *dbias, int rows, int width,
+                        void *stream) {
+    return guarded([&] {
+        require_sm100();
+        if (!x || !dy || !dx || !scale_high || !scale_low || !dscale || (kind == TG_NORM_LAYER && !dbias))
+            throw std::runtime_error("Missing norm operand");
+        if (width < 8 || width % 8 || rows < 1)
+            throw std::runtime_error("norm: width must be a positive multiple of 8");
+        cudaStream_t s = static_cast<cudaStream_t>(stream);
+        const int blocks = norm_backward_blocks(rows, device_sms());
+        float *partial = nullptr;
+        CHECK_CUDA(cudaMallocAsync(&partial, size_t(blocks) * 2 * width * sizeof(float), s));
+        NormBackwardArgs a{kind, x, dy, static_cast<const bf16 *>(scale_high), static_cast<const uint16_t *>(scale_low),
+                           residual_in, dx, partial, dscale, kind == TG_NORM_LAYER ? dbias : nullptr, rows, width, blocks};
+        launch_norm_backward(Dtype::BF16, a, s);
+        CHECK_CUDA(cudaFreeAsync(partial, s));
         CHECK_CUDA(cudaGetLastError());
     });
 }

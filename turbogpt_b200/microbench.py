@@ -105,6 +105,62 @@ def cross_entropy_case(lib, rows, iters):
     return {"kernel": "cross_entropy", "rows": rows, "us": seconds * 1e6, "gbs": bytes_moved / seconds / 1e9}
 
 
+def split_fp32(values: torch.Tensor):
+    """FP32 values as the engine stores them: high 16 bits (BF16) and low 16 bits, in separate arrays."""
+    bits = values.contiguous().view(torch.int32)
+    high = (bits >> 16).to(torch.int16).view(torch.bfloat16)
+    low = (bits & 0xffff).to(torch.int16)
+    return high.contiguous(), low.contiguous()
+
+
+def norm_case(lib, rows, width, iters, backward):
+    """LayerNorm forward (2 x rows x width x 2 B) or backward with the residual gradient
+    (x, dy, residual in, dx out: 4 x rows x width x 2 B)."""
+    g = torch.Generator(device="cuda").manual_seed(0)
+    rotate = 4  # 4 x 50 MB per tensor: beyond L2
+    make = lambda: [torch.randn(rows, width, generator=g, device="cuda").bfloat16() for _ in range(rotate)]
+    x, dy, res, out = make(), make(), make(), make()
+    scale_high, scale_low = split_fp32(1 + .1 * torch.randn(width, generator=g, device="cuda"))
+    bias_high, bias_low = split_fp32(.1 * torch.randn(width, generator=g, device="cuda"))
+    dscale, dbias = torch.empty(width, device="cuda"), torch.empty(width, device="cuda")
+    state = {"i": 0}
+
+    def forward():
+        i = state["i"] = (state["i"] + 1) % rotate
+        if lib.tg_ex_norm_forward(1, x[i].data_ptr(), scale_high.data_ptr(), scale_low.data_ptr(), bias_high.data_ptr(),
+                                  bias_low.data_ptr(), out[i].data_ptr(), rows, width, None):
+            raise RuntimeError(lib.tg_error().decode())
+
+    def back():
+        i = state["i"] = (state["i"] + 1) % rotate
+        if lib.tg_ex_norm_backward(1, x[i].data_ptr(), dy[i].data_ptr(), scale_high.data_ptr(), scale_low.data_ptr(),
+                                   res[i].data_ptr(), out[i].data_ptr(), dscale.data_ptr(), dbias.data_ptr(), rows,
+                                   width, None):
+            raise RuntimeError(lib.tg_error().decode())
+
+    seconds = _time(back if backward else forward, iters)
+    bytes_moved = rows * width * 2 * (4 if backward else 2)
+    return {"kernel": "norm_backward" if backward else "norm_forward", "rows": rows, "width": width,
+            "us": seconds * 1e6, "gbs": bytes_moved / seconds / 1e9}
+
+
+def optimizer_case(iters):
+    """The optimizer pass of BASELINE config 3 (85 M parameters: clip-norm reduction + one AdamW pass
+    over gradient, momentum, variance and the two weight halves, 28 B + 4 B per parameter) through
+    tg_optimizer_test, whose host copy of the gradient is outside the device-side profile."""
+    base = bridge.Config(depth=12, context=64, batch=1, clip=1.0)
+    ex = bridge.ConfigEx.gpt(base, 768, 12, flags=bridge.FLAG_PROFILE)
+    with bridge.Native(ex) as engine:
+        gradient = (np.random.default_rng(0).standard_normal(engine.count) * .01).astype(np.float32)
+        engine.optimizer_test(gradient, 2)
+        engine.profile(reset=True)
+        engine.optimizer_test(gradient, iters)
+        ms, launches = engine.profile()["optimizer"]
+    seconds = ms * 1e-3 / iters
+    return {"kernel": "sum_squares + adamw", "parameters": int(engine.count), "us": seconds * 1e6,
+            "gbs": engine.count * 32 / seconds / 1e9}
+
+
 def predict_case(iters):
     """Latency of tg_predict on BASELINE config 3 (one 1024-byte context through 12 layers)."""
     import time
@@ -149,6 +205,12 @@ def main() -> None:
         results.append(attention_case(lib, 32, 1024, 12, args.iters, True))
     if args.only in ("all", "cross_entropy"):
         results.append(cross_entropy_case(lib, tokens, args.iters))
+    if args.only in ("all", "norm", "norm_forward"):
+        results.append(norm_case(lib, tokens, 768, args.iters, False))
+    if args.only in ("all", "norm", "norm_backward"):
+        results.append(norm_case(lib, tokens, 768, args.iters, True))
+    if args.only in ("all", "optimizer"):
+        results.append(optimizer_case(min(args.iters, 8)))
     if args.only == "predict":
         results.append(predict_case(args.iters))
     for r in results:
