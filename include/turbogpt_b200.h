@@ -215,15 +215,17 @@ int tg_ex_attention_backward(const void *qkv, const void *out, const void *dout,
 /* RMSNorm (kind TG_NORM_RMS, eps 1e-6) or LayerNorm (TG_NORM_LAYER, eps 1e-5) over BF16 rows
  * [rows, width] (cuda/ops.cuh:56-66).  Scale and bias are FP32 values passed as the engine stores
  * them: the high 16 bits as BF16 (`*_high`) and the low 16 bits (`*_low`, uint16) in separate arrays;
- * bias pointers are ignored for RMSNorm. */
+ * bias pointers are ignored for RMSNorm.  `stats` (optional, [rows][2] floats) receives every row's
+ * mean and 1/sqrt(variance + eps) for the backward pass; it is written for widths 256, 512, 768 and
+ * 1024 (the register-resident kernels) and left untouched otherwise. */
 int tg_ex_norm_forward(int kind, const void *x, const void *scale_high, const void *scale_low, const void *bias_high,
-                       const void *bias_low, void *y, int rows, int width, void *stream);
+                       const void *bias_low, void *y, float *stats, int rows, int width, void *stream);
 /* Its backward (cuda/ops.cuh:67-80): dx = norm'(dy) rounded to BF16, plus residual_in when not NULL
  * (the running residual-stream gradient); dscale / dbias [width] FP32 are overwritten, summed over
- * rows in a fixed order. */
+ * rows in a fixed order.  `stats`: what tg_ex_norm_forward wrote for the same x (NULL: recomputed). */
 int tg_ex_norm_backward(int kind, const void *x, const void *dy, const void *scale_high, const void *scale_low,
-                        const void *residual_in, void *dx, float *dscale, float *dbias, int rows, int width,
-                        void *stream);
+                        const void *residual_in, const float *stats, void *dx, float *dscale, float *dbias, int rows,
+                        int width, void *stream);
 /* 256-way softmax cross-entropy (cuda/model.cuh:33-57): losses[rows] floats, dlogits BF16
  * = (softmax - onehot) * scale, written in place over logits when dlogits == logits. */
 int tg_ex_cross_entropy(const void *logits, const uint8_t *targets, float *losses, void *dlogits, int rows,

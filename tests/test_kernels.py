@@ -145,19 +145,23 @@ def test_norms_match_torch(rows, width, kind):
     d_x, d_dy, d_res = x.cuda(), dy.cuda(), residual.cuda()
     halves = [t.cuda() for t in (*split_fp32(scale), *split_fp32(bias))]
     y = torch.zeros_like(d_x)
+    stats = torch.zeros(rows, 2, device="cuda")
     assert lib.tg_ex_norm_forward(kind, d_x.data_ptr(), halves[0].data_ptr(), halves[1].data_ptr(), halves[2].data_ptr(),
-                                  halves[3].data_ptr(), y.data_ptr(), rows, width, None) == 0, lib.tg_error()
+                                  halves[3].data_ptr(), y.data_ptr(), stats.data_ptr(), rows, width, None) == 0, lib.tg_error()
     torch.cuda.synchronize()
     assert max_relative(y.float().cpu().numpy(), expected.detach().numpy()) <= 2.0 ** -8
     results = []
-    for _ in range(2):
+    for saved in (stats.data_ptr(), stats.data_ptr(), None):  # twice with the saved statistics, once recomputing them
         dx = torch.zeros_like(d_x)
         dscale, dbias = torch.zeros(width, device="cuda"), torch.zeros(width, device="cuda")
         assert lib.tg_ex_norm_backward(kind, d_x.data_ptr(), d_dy.data_ptr(), halves[0].data_ptr(), halves[1].data_ptr(),
-                                       d_res.data_ptr(), dx.data_ptr(), dscale.data_ptr(), dbias.data_ptr(), rows,
+                                       d_res.data_ptr(), saved, dx.data_ptr(), dscale.data_ptr(), dbias.data_ptr(), rows,
                                        width, None) == 0, lib.tg_error()
         torch.cuda.synchronize()
         results.append((dx.float().cpu().numpy(), dscale.cpu().numpy(), dbias.cpu().numpy()))
+    recomputed = results.pop()
+    assert max_relative(recomputed[0], results[0][0]) <= 2.0 ** -7
+    assert max_relative(recomputed[1], results[0][1]) <= 1e-4
     dx, dscale, dbias = results[0]
     expected_dx = residual.float() + xf.grad.bfloat16().float()  # rounded, then added to the residual gradient
     assert max_relative(dx, expected_dx.numpy()) <= 2.0 ** -7

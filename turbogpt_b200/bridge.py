@@ -179,8 +179,8 @@ def load_library() -> C.CDLL:
     lib.tg_ex_last_device_error.argtypes = [P]
     lib.tg_ex_attention_forward.argtypes = [P, P, P, I, I, I, I, I, P]
     lib.tg_ex_attention_backward.argtypes = [P, P, P, P, P, I, I, I, I, I, P]
-    lib.tg_ex_norm_forward.argtypes = [I, P, P, P, P, P, P, I, I, P]
-    lib.tg_ex_norm_backward.argtypes = [I, P, P, P, P, P, P, P, P, I, I, P]
+    lib.tg_ex_norm_forward.argtypes = [I, P, P, P, P, P, P, P, I, I, P]
+    lib.tg_ex_norm_backward.argtypes = [I, P, P, P, P, P, P, P, P, P, I, I, P]
     lib.tg_ex_cross_entropy.argtypes = [P, P, P, P, I, C.c_float, P]
     _library = lib
     return lib

@@ -58,5 +58,23 @@ def build_library(verbose: bool = False, ptxas_info: bool = False) -> Path:
     return LIBRARY
 
 
+HOST = PACKAGE / "turbogpt_dp"
+
+
+def build_host() -> Path:
+    """The data-parallel training host (host/train_dp.cpp) over the C ABI of the library."""
+    source = PACKAGE / "host" / "train_dp.cpp"
+    if _stale(HOST, [source, PACKAGE.parent / "include" / "turbogpt_b200.h", LIBRARY]):
+        staged = HOST.with_name(HOST.name + ".staged")
+        cmd = ["g++", "-O2", "-std=c++17", "-pthread", str(source), f"-L{PACKAGE}", "-lturbogpt_b200",
+               "-Wl,-rpath,$ORIGIN", "-o", str(staged)]
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode:
+            raise RuntimeError(f"host build failed:\n{r.stdout}\n{r.stderr}")
+        os.replace(staged, HOST)
+    return HOST
+
+
 if __name__ == "__main__":
     print(build_library(verbose=True, ptxas_info="--ptxas" in sys.argv))
+    print(build_host())

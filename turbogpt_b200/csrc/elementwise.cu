@@ -3,6 +3,7 @@
 // with 128-bit accesses; rows are handled by one warp so the row statistics are shuffle
 // reductions.
 #include "device_utils.cuh"
+#include <atomic>
 #include "kernels.cuh"
 #include "sm100.cuh"
 
@@ -578,14 +579,14 @@ template <class T, int V> __global__ void __launch_bounds__(256, 2) norm_backwar
 }
 template <class T, int V> static void launch_norm_backward_rows(const NormBackwardArgs &a, cudaStream_t s) {
     const size_t shared = size_t(V * 256 + 8 * 2 * a.width) * sizeof(float);
-    static unsigned long long configured = 0; // one bit per device; this instantiation's own
+    static std::atomic<unsigned long long> configured{0}; // one bit per device; engines on other devices run on other threads
     int device = 0;
     CHECK_CUDA(cudaGetDevice(&device));
-    if (shared > 48 * 1024 && (device >= 64 || !(configured >> device & 1))) {
+    if (shared > 48 * 1024 && (device >= 64 || !(configured.load() >> device & 1))) {
         CHECK_CUDA(cudaFuncSetAttribute(norm_backward_rows_kernel<T, V>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                         int(shared)));
         if (device < 64)
-            configured |= 1ull << device;
+            configured.fetch_or(1ull << device);
     }
     norm_backward_rows_kernel<T, V><<<a.blocks, 256, shared, s>>>(a);
 }

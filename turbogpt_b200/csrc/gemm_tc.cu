@@ -88,13 +88,6 @@ __device__ __forceinline__ void store_group(const TcParams &p, float (&v)[8], lo
         store8((float *)p.c + ci, v);
         return;
     }
-    if (p.epilogue == int(Epilogue::Residual) || p.epilogue == int(Epilogue::GeluGrad)) {
-        float r[8];
-        load8((const bf16 *)p.r + ri, r);
-#pragma unroll
-        for (int j = 0; j < 8; ++j)
-            v[j] = p.epilogue == int(Epilogue::Residual) ? rounded<bf16>(v[j]) + r[j] : rounded<bf16>(v[j]) * r[j];
-    }
     store8((bf16 *)p.c + ci, v);
 }
 
@@ -523,7 +516,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 // ---------------------------------------------------------------------------- host side ------
 struct Schedule {
     int bn = 0, splits = 1, k_blocks_per_split = 0, pair = 0;
-    long long time = 0, rounds = 0, items = 0, slots = 0; // the cost model's estimate and the round count it rests on
 };
 
 // Tile width, K splits and single CTA / CTA pair by a small cost model, in clocks per 64-deep K
@@ -532,8 +524,7 @@ struct Schedule {
 // first: they halve the B bytes each SM stages per K block.
 Schedule choose_schedule(const GemmArgs &g, int sms) {
     const bool b_mn = g.b_col != 1;
-    // the split-K reduction applies Store, +residual, x saved derivative and FP32 axpby; GELU (two outputs) is not split
-    const bool unsplittable = g.epilogue == Epilogue::GeluDual || (g.epilogue == Epilogue::Axpby && g.out != Dtype::FP32);
+    const bool second_tensor = g.epilogue != Epilogue::Store; // K is split only for plain stores
     const int m_tiles = (g.m + BM - 1) / BM, k_blocks = (g.k + BK - 1) / BK;
     Schedule best;
     long long best_time = 0;
@@ -553,17 +544,16 @@ Schedule choose_schedule(const GemmArgs &g, int sms) {
             const int mma = bn / 2 > (128 + bn) / 4 ? bn / 2 : (128 + bn) / 4;
             const int block_cost = unit == 2 ? mma + 16 : mma * (k_blocks >= 64 ? 9 : 11) / 8 + 16;
             for (int splits : {1, 2, 3, 4, 6, 8, 12, 16}) {
-                if (splits > 1 && (k_blocks / splits < 8 || tiles * splits > slots || unsplittable))
+                if (splits > 1 && (k_blocks / splits < 8 || tiles * splits > slots || second_tensor))
                     continue;
                 const int per = (k_blocks + splits - 1) / splits;
                 if (splits > 1 && (k_blocks + per - 1) / per != splits)
                     continue; // would leave an empty split
                 const long long rounds = (tiles * splits + slots - 1) / slots;
                 const long long time = rounds * ((long long)per * block_cost + bn + (splits > 1 ? splits * bn / 2 : 0));
-                if (!best.bn || time < best_time) {
-                    best.bn = bn, best.splits = splits, best.k_blocks_per_split = per, best.pair = unit == 2;
-                    best.time = best_time = time, best.rounds = rounds, best.items = tiles * splits, best.slots = slots;
-                }
+                if (!best.bn || time < best_time)
+                    best.bn = bn, best.splits = splits, best.k_blocks_per_split = per, best.pair = unit == 2,
+                    best_time = time;
             }
         }
     }
@@ -750,34 +740,6 @@ void release_gemm_workspace(GemmWorkspace &w) {
 // whose device-side give-ups are reported by gemm_tc_take_device_error().
 void launch_gemm_tc(const GemmArgs &g, int sms, StepCounters *counters, cudaStream_t s, GemmWorkspace *workspace) {
     const Schedule sc = choose_schedule(g, sms);
-    // A last round that fills only part of the machine (e.g. 384 tiles on 74 CTA pairs: 5.19 rounds cost
-    // 6) is cut off: the rows of the whole rounds go in one launch, the remaining rows in a second one
-    // whose few tiles are split along K over all SMs.  Only for a K-major A (rows of A = rows of C).
-    if (sc.splits == 1 && g.batch == 1 && g.a_col == 1 && sc.rounds >= 3 && sc.items % sc.slots != 0) {
-        const int unit_rows = BM * (sc.pair ? 2 : 1);
-        const long long n_tiles = (g.n + sc.bn - 1) / sc.bn, m_units = (g.m + unit_rows - 1) / unit_rows;
-        const long long head_units = (sc.rounds - 1) * sc.slots / n_tiles;
-        if (head_units >= 1 && head_units < m_units) {
-            GemmArgs head = g, tail = g;
-            const long long row = head_units * unit_rows;
-            const size_t element = g.out == Dtype::FP32 ? 4 : 2;
-            head.m = int(row);
-            tail.m = g.m - int(row);
-            tail.a = static_cast<const char *>(g.a) + row * g.a_row * 2;
-            tail.c = static_cast<char *>(g.c) + row * g.ldc * element;
-            if (g.r)
-                tail.r = static_cast<const char *>(g.r) + row * g.ldr * (g.epilogue == Epilogue::GeluGrad ? 2 : element);
-            if (g.c2)
-                tail.c2 = static_cast<char *>(g.c2) + row * g.ldc * 2;
-            const Schedule head_sc = choose_schedule(head, sms), tail_sc = choose_schedule(tail, sms);
-            constexpr long long LaunchCost = 1500; // a second launch (drain, fill, set-up), in the cost model's units
-            if (head_sc.time + tail_sc.time + LaunchCost < sc.time && gemm_tc_supported(tail)) {
-                launch_with(head, head_sc, sms, counters, s, workspace);
-                launch_with(tail, tail_sc, sms, counters, s, workspace);
-                return;
-            }
-        }
-    }
     launch_with(g, sc, sms, counters, s, workspace);
 }
 

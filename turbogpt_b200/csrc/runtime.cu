@@ -360,7 +360,7 @@ int tg_ex_attention_backward(const void *qkv, const void *out, const void *dout,
     });
 }
 int tg_ex_norm_forward(int kind, const void *x, const void *scale_high, const void *scale_low, const void *bias_high,
-                       const void *bias_low, void *y, int rows, int width, void *stream) {
+                       const void *bias_low, void *y, float *stats, int rows, int width, void *stream) {
     return guarded([&] {
         require_sm100();
         if (!x || !y || !scale_high || !scale_low || (kind == TG_NORM_LAYER && (!bias_high || !bias_low)))
@@ -370,14 +370,15 @@ int tg_ex_norm_forward(int kind, const void *x, const void *scale_high, const vo
         NormArgs a{kind, x, static_cast<const bf16 *>(scale_high),
                    kind == TG_NORM_LAYER ? static_cast<const bf16 *>(bias_high) : nullptr,
                    static_cast<const uint16_t *>(scale_low),
-                   kind == TG_NORM_LAYER ? static_cast<const uint16_t *>(bias_low) : nullptr, y, rows, width};
+                   kind == TG_NORM_LAYER ? static_cast<const uint16_t *>(bias_low) : nullptr, y, rows, width,
+                   width % 256 == 0 && width <= 1024 ? stats : nullptr};
         launch_norm(Dtype::BF16, a, static_cast<cudaStream_t>(stream));
         CHECK_CUDA(cudaGetLastError());
     });
 }
 int tg_ex_norm_backward(int kind, const void *x, const void *dy, const void *scale_high, const void *scale_low,
-                        const void *residual_in, void *dx, float *dscale, float *dbias, int rows, int width,
-                        void *stream) {
+                        const void *residual_in, const float *stats, void *dx, float *dscale, float *dbias, int rows,
+                        int width, void *stream) {
     return guarded([&] {
         require_sm100();
         if (!x || !dy || !dx || !scale_high || !scale_low || !dscale || (kind == TG_NORM_LAYER && !dbias))
@@ -389,7 +390,8 @@ int tg_ex_norm_backward(int kind, const void *x, const void *dy, const void *sca
         float *partial = nullptr;
         CHECK_CUDA(cudaMallocAsync(&partial, size_t(blocks) * 2 * width * sizeof(float), s));
         NormBackwardArgs a{kind, x, dy, static_cast<const bf16 *>(scale_high), static_cast<const uint16_t *>(scale_low),
-                           residual_in, dx, partial, dscale, kind == TG_NORM_LAYER ? dbias : nullptr, rows, width, blocks};
+                           residual_in, dx, partial, dscale, kind == TG_NORM_LAYER ? dbias : nullptr, rows, width, blocks,
+                           width % 256 == 0 && width <= 1024 ? stats : nullptr};
         launch_norm_backward(Dtype::BF16, a, s);
         CHECK_CUDA(cudaFreeAsync(partial, s));
         CHECK_CUDA(cudaGetLastError());

@@ -123,20 +123,24 @@ def norm_case(lib, rows, width, iters, backward):
     scale_high, scale_low = split_fp32(1 + .1 * torch.randn(width, generator=g, device="cuda"))
     bias_high, bias_low = split_fp32(.1 * torch.randn(width, generator=g, device="cuda"))
     dscale, dbias = torch.empty(width, device="cuda"), torch.empty(width, device="cuda")
+    stats = [torch.empty(rows, 2, device="cuda") for _ in range(rotate)]
     state = {"i": 0}
 
     def forward():
         i = state["i"] = (state["i"] + 1) % rotate
         if lib.tg_ex_norm_forward(1, x[i].data_ptr(), scale_high.data_ptr(), scale_low.data_ptr(), bias_high.data_ptr(),
-                                  bias_low.data_ptr(), out[i].data_ptr(), rows, width, None):
+                                  bias_low.data_ptr(), out[i].data_ptr(), stats[i].data_ptr(), rows, width, None):
             raise RuntimeError(lib.tg_error().decode())
 
     def back():
         i = state["i"] = (state["i"] + 1) % rotate
         if lib.tg_ex_norm_backward(1, x[i].data_ptr(), dy[i].data_ptr(), scale_high.data_ptr(), scale_low.data_ptr(),
-                                   res[i].data_ptr(), out[i].data_ptr(), dscale.data_ptr(), dbias.data_ptr(), rows,
-                                   width, None):
+                                   res[i].data_ptr(), stats[i].data_ptr(), out[i].data_ptr(), dscale.data_ptr(),
+                                   dbias.data_ptr(), rows, width, None):
             raise RuntimeError(lib.tg_error().decode())
+
+    for _ in range(rotate):  # the backward pass reads the statistics the forward pass left
+        forward()
 
     seconds = _time(back if backward else forward, iters)
     bytes_moved = rows * width * 2 * (4 if backward else 2)
@@ -159,6 +163,41 @@ def optimizer_case(iters):
     seconds = ms * 1e-3 / iters
     return {"kernel": "sum_squares + adamw", "parameters": int(engine.count), "us": seconds * 1e6,
             "gbs": engine.count * 32 / seconds / 1e9}
+
+
+def muon_case(iters):
+    """Muon on the hidden matrices of BASELINE config 3's shapes (prepare, normalise, five Newton-Schulz
+    iterations as batched tcgen05 GEMMs, apply) plus AdamW on the rest, through tg_optimizer_test."""
+    base = bridge.Config(depth=12, context=64, batch=1, clip=1.0, ns_steps=5)
+    ex = bridge.ConfigEx.gpt(base, 768, 12, flags=bridge.FLAG_PROFILE, hidden_optimizer=bridge.HIDDEN_MUON)
+    with bridge.Native(ex) as engine:
+        gradient = (np.random.default_rng(0).standard_normal(engine.count) * .01).astype(np.float32)
+        engine.optimizer_test(gradient, 1)
+        engine.profile(reset=True)
+        engine.optimizer_test(gradient, iters)
+        families = engine.profile()
+    return {"kernel": "muon (5 Newton-Schulz iterations) + adamw", "parameters": int(engine.count),
+            "muon_us": families["muon"][0] * 1e3 / iters, "muon_launches": families["muon"][1] // iters,
+            "adamw_us": families["optimizer"][0] * 1e3 / iters}
+
+
+def embedding_case(iters):
+    """Embedding gather and its deterministic scatter-add inside a small engine (8 x 1024 tokens, d 768):
+    a forward/backward pass through tg_batch, timed per kernel family."""
+    base = bridge.Config(depth=1, context=1024, batch=8, clip=0)
+    ex = bridge.ConfigEx.gpt(base, 768, 12, flags=bridge.FLAG_PROFILE)
+    rng = np.random.default_rng(0)
+    x = rng.integers(0, 256, (8, 1024), dtype=np.uint8)
+    with bridge.Native(ex) as engine:
+        engine.set_weights(bridge.initialize_weights(ex))
+        engine.batch(x, x)
+        engine.profile(reset=True)
+        for _ in range(iters):
+            engine.batch(x, x)
+        families = engine.profile()
+    tokens = 8 * 1024
+    return {"kernel": "embedding gather / scatter", "tokens": tokens,
+            "gather_us": families["embedding"][0] * 1e3 / iters, "scatter_us": families["embedding_backward"][0] * 1e3 / iters}
 
 
 def predict_case(iters):
@@ -211,6 +250,10 @@ def main() -> None:
         results.append(norm_case(lib, tokens, 768, args.iters, True))
     if args.only in ("all", "optimizer"):
         results.append(optimizer_case(min(args.iters, 8)))
+    if args.only == "muon":
+        results.append(muon_case(min(args.iters, 4)))
+    if args.only == "embedding":
+        results.append(embedding_case(min(args.iters, 8)))
     if args.only == "predict":
         results.append(predict_case(args.iters))
     for r in results:
