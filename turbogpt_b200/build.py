@@ -10,7 +10,7 @@ from pathlib import Path
 PACKAGE = Path(__file__).resolve().parent
 CSRC = PACKAGE / "csrc"
 LIBRARY = PACKAGE / "libturbogpt_b200.so"
-SOURCES = ["host.cpp", "checkpoint.cpp", "elementwise.cu", "attention_simt.cu", "gemm_simt.cu", "gemm_tc.cu", "attention_tc.cu", "optim.cu",
+SOURCES = ["host.cpp", "checkpoint.cpp", "elementwise.cu", "attention_simt.cu", "gemm_simt.cu", "gemm_tc.cu", "attention_tc.cu", "attention_bwd_fused.cu", "optim.cu",
            "selftest.cu", "engine.cu", "runtime.cu"]
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
          "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=default", "--expt-relaxed-constexpr"]

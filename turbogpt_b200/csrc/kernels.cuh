@@ -112,6 +112,14 @@ void launch_flash_attention_backward(const void *qkv, const void *out, const voi
                                      float *delta, void *dqkv, int batch, int context, int heads,
                                      StepCounters *counters, cudaStream_t s);
 
+// One fused kernel for dQ, dK and dV (attention_bwd_fused.cu): every probability is exponentiated once.
+// `scratch` (flash_backward_scratch_bytes) holds the FP32 running sums of dQ between key tiles and their
+// counters; `delta` as above.
+size_t flash_backward_scratch_bytes(int batch, int context, int heads);
+void launch_flash_attention_backward_fused(const void *qkv, const void *out, const void *dout, const float *lse,
+                                           float *delta, void *dqkv, void *scratch, int batch, int context, int heads,
+                                           StepCounters *counters, cudaStream_t s);
+
 // ---- MLP activations (reference cuda/ops.cuh:118-144) ----
 // wide: [tokens, 2*hidden] = gate | up.  out: [tokens, hidden].
 void launch_swiglu(Dtype t, const void *wide, void *out, int tokens, int hidden, cudaStream_t s);

@@ -141,8 +141,91 @@ __global__ void __launch_bounds__(256) muon_prepare_kernel(MuonPrepareArgs a) {
     if (threadIdx.x == 0)
         a.sumsq[matrix * MuonBlocks + blockIdx.x] = squares;
 }
+// The same stage, 128-bit: eight consecutive elements per thread (matrices stored in the orientation the
+// iterations use, rows <= cols).
+__global__ void __launch_bounds__(256) muon_prepare_vector_kernel(MuonPrepareArgs a) {
+    __shared__ float scratch[32];
+    const float clip = clip_factor(a.norm_partial, a.norm_blocks, a.clip, scratch);
+    float mu = a.momentum_rate;
+    if (a.schedule)
+        mu = a.schedule[a.counters->step].momentum;
+    const int matrix = blockIdx.y;
+    const int64_t size = int64_t(a.rows) * a.cols, base = matrix * a.stride;
+    float squares = 0;
+    for (int64_t i = (blockIdx.x * int64_t(blockDim.x) + threadIdx.x) * 8; i < size;
+         i += int64_t(gridDim.x) * blockDim.x * 8) {
+        float g[8], m[8], u[8];
+        load8(a.gradient + base + i, g);
+        load8(a.momentum + base + i, m);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            g[j] *= clip;
+            m[j] += (1 - mu) * (g[j] - m[j]);
+            u[j] = rounded<bf16>(g[j] + mu * (m[j] - g[j]));
+            squares += u[j] * u[j];
+        }
+        store8(a.momentum + base + i, m);
+        store8(a.x + matrix * size + i, u);
+    }
+    squares = block_sum(squares, scratch);
+    if (threadIdx.x == 0)
+        a.sumsq[matrix * MuonBlocks + blockIdx.x] = squares;
+}
+// Tall matrices (rows > cols) are orthogonalised transposed.  64 x 64 tiles go through shared memory so
+// that gradient and momentum are read, and the transposed BF16 matrix written, in whole 128-byte lines.
+constexpr int MuonTile = 64, MuonTilePitch = 66; // BF16 elements per tile row in shared memory (33 words: spreads the banks)
+__global__ void __launch_bounds__(256) muon_prepare_transpose_kernel(MuonPrepareArgs a) {
+    __shared__ float scratch[32];
+    __shared__ __align__(16) bf16 tile[MuonTile * MuonTilePitch]; // [column][row]
+    const float clip = clip_factor(a.norm_partial, a.norm_blocks, a.clip, scratch);
+    float mu = a.momentum_rate;
+    if (a.schedule)
+        mu = a.schedule[a.counters->step].momentum;
+    const int matrix = blockIdx.y;
+    const int64_t size = int64_t(a.rows) * a.cols, base = matrix * a.stride;
+    const int tiles_across = a.cols / MuonTile, tiles = (a.rows / MuonTile) * tiles_across;
+    float squares = 0;
+    for (int t = blockIdx.x; t < tiles; t += gridDim.x) {
+        const int r0 = t / tiles_across * MuonTile, c0 = t % tiles_across * MuonTile;
+        for (int item = threadIdx.x; item < MuonTile * 8; item += blockDim.x) { // (row, group of 8 columns)
+            const int rr = item / 8, chunk = item % 8;
+            const int64_t at = base + int64_t(r0 + rr) * a.cols + c0 + chunk * 8;
+            float g[8], m[8];
+            load8(a.gradient + at, g);
+            load8(a.momentum + at, m);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                g[j] *= clip;
+                m[j] += (1 - mu) * (g[j] - m[j]);
+                const bf16 u = __float2bfloat16_rn(g[j] + mu * (m[j] - g[j]));
+                tile[(chunk * 8 + j) * MuonTilePitch + rr] = u;
+                squares += __bfloat162float(u) * __bfloat162float(u);
+            }
+            store8(a.momentum + at, m);
+        }
+        __syncthreads();
+        for (int item = threadIdx.x; item < MuonTile * 8; item += blockDim.x) { // (column, group of 8 rows)
+            const int cc = item / 8, chunk = item % 8;
+            const uint32_t *source = reinterpret_cast<const uint32_t *>(tile + cc * MuonTilePitch + chunk * 8);
+            *reinterpret_cast<uint4 *>(a.x + matrix * size + int64_t(c0 + cc) * a.rows + r0 + chunk * 8) =
+                make_uint4(source[0], source[1], source[2], source[3]);
+        }
+        __syncthreads();
+    }
+    squares = block_sum(squares, scratch);
+    if (threadIdx.x == 0)
+        a.sumsq[matrix * MuonBlocks + blockIdx.x] = squares;
+}
 void launch_muon_prepare(const MuonPrepareArgs &a, cudaStream_t s) {
-    muon_prepare_kernel<<<dim3(MuonBlocks, a.batch), 256, 0, s>>>(a);
+    const dim3 grid(MuonBlocks, a.batch);
+    const bool aligned = a.stride % 8 == 0 && reinterpret_cast<uintptr_t>(a.gradient) % 32 == 0 &&
+                         reinterpret_cast<uintptr_t>(a.momentum) % 32 == 0;
+    if (aligned && a.rows > a.cols && a.rows % MuonTile == 0 && a.cols % MuonTile == 0)
+        muon_prepare_transpose_kernel<<<grid, 256, 0, s>>>(a);
+    else if (aligned && a.rows <= a.cols && (int64_t(a.rows) * a.cols) % 8 == 0)
+        muon_prepare_vector_kernel<<<grid, 256, 0, s>>>(a);
+    else
+        muon_prepare_kernel<<<grid, 256, 0, s>>>(a);
 }
 // x /= max(bf16(|x|_F), bf16(1e-7)), rounded to BF16.
 __global__ void __launch_bounds__(256) muon_normalize_kernel(bf16 *x, const float *sumsq, int64_t per_matrix) {
@@ -156,8 +239,28 @@ __global__ void __launch_bounds__(256) muon_normalize_kernel(bf16 *x, const floa
          i += int64_t(gridDim.x) * blockDim.x)
         x[matrix * per_matrix + i] = __float2bfloat16_rn(__bfloat162float(x[matrix * per_matrix + i]) / norm);
 }
+__global__ void __launch_bounds__(256) muon_normalize_vector_kernel(bf16 *x, const float *sumsq, int64_t per_matrix) {
+    const int matrix = blockIdx.y;
+    float total = 0;
+    for (int b = 0; b < MuonBlocks; ++b)
+        total += sumsq[matrix * MuonBlocks + b];
+    const float norm = fmaxf(__bfloat162float(__float2bfloat16_rn(sqrtf(total))),
+                             __bfloat162float(__float2bfloat16_rn(1e-7f)));
+    for (int64_t i = (blockIdx.x * int64_t(blockDim.x) + threadIdx.x) * 8; i < per_matrix;
+         i += int64_t(gridDim.x) * blockDim.x * 8) {
+        float v[8];
+        load8(x + matrix * per_matrix + i, v);
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+            v[j] /= norm;
+        store8(x + matrix * per_matrix + i, v);
+    }
+}
 void launch_muon_normalize(bf16 *x, const float *sumsq, int64_t per_matrix, int batch, cudaStream_t s) {
-    muon_normalize_kernel<<<dim3(MuonBlocks, batch), 256, 0, s>>>(x, sumsq, per_matrix);
+    if (per_matrix % 8 == 0 && reinterpret_cast<uintptr_t>(x) % 16 == 0)
+        muon_normalize_vector_kernel<<<dim3(MuonBlocks, batch), 256, 0, s>>>(x, sumsq, per_matrix);
+    else
+        muon_normalize_kernel<<<dim3(MuonBlocks, batch), 256, 0, s>>>(x, sumsq, per_matrix);
 }
 // w = w * (1 - lr * wd) - lr * sqrt(max(1, rows/cols)) * x, x transposed back when rows > cols.
 __global__ void __launch_bounds__(256) muon_apply_kernel(MuonApplyArgs a) {
@@ -181,8 +284,91 @@ __global__ void __launch_bounds__(256) muon_apply_kernel(MuonApplyArgs a) {
             a.weight_fp32[base + i] = w;
     }
 }
+// Eight consecutive weights per thread: both 16-bit halves of the FP32 masters as 128-bit accesses.
+__device__ __forceinline__ void muon_update8(const MuonApplyArgs &a, int64_t at, const float (&x)[8], float keep,
+                                             float adjusted) {
+    const uint4 high = *reinterpret_cast<const uint4 *>(a.weight_high + at);
+    const uint4 low = *reinterpret_cast<const uint4 *>(a.weight_low + at);
+    const unsigned h[4] = {high.x, high.y, high.z, high.w}, l[4] = {low.x, low.y, low.z, low.w};
+    unsigned ho[4], lo[4];
+    float w[8];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        w[2 * j] = __uint_as_float((h[j] << 16) | (l[j] & 0xffffu));
+        w[2 * j + 1] = __uint_as_float((h[j] & 0xffff0000u) | (l[j] >> 16));
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        w[j] *= keep;
+        w[j] -= adjusted * x[j];
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const unsigned b0 = __float_as_uint(w[2 * j]), b1 = __float_as_uint(w[2 * j + 1]);
+        ho[j] = (b0 >> 16) | (b1 & 0xffff0000u);
+        lo[j] = (b0 & 0xffffu) | (b1 << 16);
+    }
+    *reinterpret_cast<uint4 *>(a.weight_high + at) = make_uint4(ho[0], ho[1], ho[2], ho[3]);
+    *reinterpret_cast<uint4 *>(a.weight_low + at) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+    if (a.weight_fp32)
+        store8(a.weight_fp32 + at, w);
+}
+__global__ void __launch_bounds__(256) muon_apply_vector_kernel(MuonApplyArgs a) {
+    float multiplier = 1;
+    if (a.schedule)
+        multiplier = a.schedule[a.counters->step].multiplier;
+    const float lr = a.muon_lr * multiplier;
+    const float adjusted = lr * sqrtf(fmaxf(1.f, float(a.rows) / a.cols)), keep = 1 - lr * a.weight_decay;
+    const int matrix = blockIdx.y;
+    const int64_t size = int64_t(a.rows) * a.cols, base = matrix * a.stride;
+    for (int64_t i = (blockIdx.x * int64_t(blockDim.x) + threadIdx.x) * 8; i < size;
+         i += int64_t(gridDim.x) * blockDim.x * 8) {
+        float x[8];
+        load8(a.x + matrix * size + i, x);
+        muon_update8(a, base + i, x, keep, adjusted);
+    }
+}
+__global__ void __launch_bounds__(256) muon_apply_transpose_kernel(MuonApplyArgs a) {
+    __shared__ __align__(16) bf16 tile[MuonTile * MuonTilePitch]; // [column][row], as stored
+    float multiplier = 1;
+    if (a.schedule)
+        multiplier = a.schedule[a.counters->step].multiplier;
+    const float lr = a.muon_lr * multiplier;
+    const float adjusted = lr * sqrtf(fmaxf(1.f, float(a.rows) / a.cols)), keep = 1 - lr * a.weight_decay;
+    const int matrix = blockIdx.y;
+    const int64_t size = int64_t(a.rows) * a.cols, base = matrix * a.stride;
+    const int tiles_across = a.cols / MuonTile, tiles = (a.rows / MuonTile) * tiles_across;
+    for (int t = blockIdx.x; t < tiles; t += gridDim.x) {
+        const int r0 = t / tiles_across * MuonTile, c0 = t % tiles_across * MuonTile;
+        for (int item = threadIdx.x; item < MuonTile * 8; item += blockDim.x) { // (column, group of 8 rows)
+            const int cc = item / 8, chunk = item % 8;
+            const uint4 v = *reinterpret_cast<const uint4 *>(a.x + matrix * size + int64_t(c0 + cc) * a.rows + r0 + chunk * 8);
+            uint32_t *target = reinterpret_cast<uint32_t *>(tile + cc * MuonTilePitch + chunk * 8);
+            target[0] = v.x, target[1] = v.y, target[2] = v.z, target[3] = v.w;
+        }
+        __syncthreads();
+        for (int item = threadIdx.x; item < MuonTile * 8; item += blockDim.x) { // (row, group of 8 columns)
+            const int rr = item / 8, chunk = item % 8;
+            float x[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                x[j] = __bfloat162float(tile[(chunk * 8 + j) * MuonTilePitch + rr]);
+            muon_update8(a, base + int64_t(r0 + rr) * a.cols + c0 + chunk * 8, x, keep, adjusted);
+        }
+        __syncthreads();
+    }
+}
 void launch_muon_apply(const MuonApplyArgs &a, cudaStream_t s) {
-    muon_apply_kernel<<<dim3(MuonBlocks, a.batch), 256, 0, s>>>(a);
+    const dim3 grid(MuonBlocks, a.batch);
+    const bool aligned = a.stride % 8 == 0 && reinterpret_cast<uintptr_t>(a.weight_high) % 16 == 0 &&
+                         reinterpret_cast<uintptr_t>(a.weight_low) % 16 == 0 &&
+                         reinterpret_cast<uintptr_t>(a.weight_fp32) % 32 == 0 && reinterpret_cast<uintptr_t>(a.x) % 16 == 0;
+    if (aligned && a.rows > a.cols && a.rows % MuonTile == 0 && a.cols % MuonTile == 0)
+        muon_apply_transpose_kernel<<<grid, 256, 0, s>>>(a);
+    else if (aligned && a.rows <= a.cols && (int64_t(a.rows) * a.cols) % 8 == 0)
+        muon_apply_vector_kernel<<<grid, 256, 0, s>>>(a);
+    else
+        muon_apply_kernel<<<grid, 256, 0, s>>>(a);
 }
 
 __global__ void advance_kernel(StepCounters *counters) {

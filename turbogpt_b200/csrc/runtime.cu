@@ -350,8 +350,17 @@ int tg_ex_attention_backward(const void *qkv, const void *out, const void *dout,
                                    static_cast<cudaStream_t>(stream)));
         SoftmaxAttentionBackwardArgs a{qkv, out, dout, lse, delta, dqkv, batch, context, heads * d_head, heads};
         if (tensor_cores) {
+#ifndef TG_TWO_KERNEL_ATTENTION_BACKWARD
+            void *scratch = nullptr;
+            CHECK_CUDA(cudaMallocAsync(&scratch, flash_backward_scratch_bytes(batch, context, heads),
+                                       static_cast<cudaStream_t>(stream)));
+            launch_flash_attention_backward_fused(qkv, out, dout, lse, delta, dqkv, scratch, batch, context, heads,
+                                                  nullptr, static_cast<cudaStream_t>(stream));
+            CHECK_CUDA(cudaFreeAsync(scratch, static_cast<cudaStream_t>(stream)));
+#else
             launch_flash_attention_backward(qkv, out, dout, lse, delta, dqkv, batch, context, heads, nullptr,
                                             static_cast<cudaStream_t>(stream));
+#endif
         } else {
             launch_softmax_attention_backward(Dtype::BF16, a, static_cast<cudaStream_t>(stream));
         }
