@@ -209,6 +209,11 @@ int tg_ex_last_device_error(void *stream);
  * out [batch*context, heads*d_head]; lse [batch, heads, context] floats. */
 int tg_ex_attention_forward(const void *qkv, void *out, float *lse, int batch, int context, int heads,
                             int d_head, int tensor_cores, void *stream);
+/* tensor_cores: 0 = SIMT kernels; 1 = the engine's tensor-core kernels (dQ by query tile, then dK and dV by key
+ * tile); TG_ATTENTION_BACKWARD_SINGLE_PASS = one tensor-core kernel that forms dQ, dK and dV from a single
+ * pass over the score blocks (same results up to rounding; slower at the measured shapes, kept for comparison).
+ * The tensor-core forms keep one grow-only scratch allocation per device; calls on a device must not overlap. */
+#define TG_ATTENTION_BACKWARD_SINGLE_PASS 2
 int tg_ex_attention_backward(const void *qkv, const void *out, const void *dout, const float *lse,
                              void *dqkv, int batch, int context, int heads, int d_head, int tensor_cores,
                              void *stream);

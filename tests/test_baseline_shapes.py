@@ -76,8 +76,9 @@ def _attention_reference(qkv, dout, batch, context, heads, pairs):
     return expected
 
 
+@pytest.mark.parametrize("form", [1, 2], ids=["engine_form", "single_pass"])
 @pytest.mark.parametrize("batch,context,heads", [(32, 1024, 12), (2, 4096, 2)])
-def test_attention_at_benchmark_size(batch, context, heads):
+def test_attention_at_benchmark_size(batch, context, heads, form):
     lib = load_library()
     width = heads * 64
     g = torch.Generator(device="cuda").manual_seed(0)
@@ -89,7 +90,7 @@ def test_attention_at_benchmark_size(batch, context, heads):
     assert lib.tg_ex_attention_forward(qkv.data_ptr(), out.data_ptr(), lse.data_ptr(), batch, context, heads, 64, 1,
                                        None) == 0, lib.tg_error()
     assert lib.tg_ex_attention_backward(qkv.data_ptr(), out.data_ptr(), dout.data_ptr(), lse.data_ptr(),
-                                        dqkv.data_ptr(), batch, context, heads, 64, 1, None) == 0, lib.tg_error()
+                                        dqkv.data_ptr(), batch, context, heads, 64, form, None) == 0, lib.tg_error()
     torch.cuda.synchronize()
     pairs = sorted({(0, 0), (batch - 1, heads - 1), (batch // 2, heads // 2), (1, heads - 1), (batch - 1, 0)})
     expected = _attention_reference(qkv, dout, batch, context, heads, pairs)
@@ -106,7 +107,7 @@ def test_attention_at_benchmark_size(batch, context, heads):
     # deterministic: a second backward gives the same bits
     again = torch.zeros_like(qkv)
     assert lib.tg_ex_attention_backward(qkv.data_ptr(), out.data_ptr(), dout.data_ptr(), lse.data_ptr(),
-                                        again.data_ptr(), batch, context, heads, 64, 1, None) == 0, lib.tg_error()
+                                        again.data_ptr(), batch, context, heads, 64, form, None) == 0, lib.tg_error()
     torch.cuda.synchronize()
     assert torch.equal(again, dqkv)
 

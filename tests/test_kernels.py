@@ -113,12 +113,13 @@ def test_attention_matches_torch(batch, context, heads, d_head):
         np.testing.assert_allclose(lse.cpu().numpy(), expected_lse, rtol=1e-4, atol=1e-4)
         if tensor_cores and not BACKWARD_ON_TENSOR_CORES:
             continue
-        d_dqkv.zero_()
-        assert lib.tg_ex_attention_backward(d_qkv.data_ptr(), d_out.data_ptr(), d_dout.data_ptr(), lse.data_ptr(),
-                                            d_dqkv.data_ptr(), batch, context, heads, d_head, tensor_cores, None) == 0, \
-            lib.tg_error()
-        torch.cuda.synchronize()
-        assert max_relative(d_dqkv.float().cpu().numpy(), expected_dqkv) <= 1e-2, tensor_cores
+        for form in ((1, 2) if tensor_cores else (0,)):  # 2: the single-pass tensor-core kernel
+            d_dqkv.zero_()
+            assert lib.tg_ex_attention_backward(d_qkv.data_ptr(), d_out.data_ptr(), d_dout.data_ptr(), lse.data_ptr(),
+                                                d_dqkv.data_ptr(), batch, context, heads, d_head, form, None) == 0, \
+                lib.tg_error()
+            torch.cuda.synchronize()
+            assert max_relative(d_dqkv.float().cpu().numpy(), expected_dqkv) <= 1e-2, form
 
 
 @pytest.mark.parametrize("rows,width", [(1000, 768), (515, 256), (300, 1024), (64, 96)])

@@ -1,7 +1,15 @@
-// Fused backward of causal softmax attention, head size 64, BF16: dQ, dK and dV from ONE pass over the
-// score blocks, so every probability is exponentiated once (a dq kernel followed by a dk/dv kernel
+// Single-pass backward of causal softmax attention, head size 64, BF16: dQ, dK and dV from ONE pass over
+// the score blocks, so every probability is exponentiated once (a dq kernel followed by a dk/dv kernel
 // evaluates each twice and repeats the S = Q K^T and dP = dO V^T products).  Same role as the
 // reference's attention_backward loops (cuda/attention.cuh:69-106), nothing of their structure.
+// The engine runs the two-kernel form (attention_tc.cu): measured on B200, this kernel takes 420 us
+// against 349 us at 32 x 12 x 1024, 1076 against 935 at 8 x 12 x 4096, 306 against 262 at 64 x 12 x 512
+// (both with their statistics kernels).  It is reachable through tg_ex_attention_backward for comparison.
+// Where the time goes: tensor memory (512 columns) only leaves room for 64-query steps, whose
+// 128 x 64 x 16 products re-read their 4 KB A operand from shared memory every instruction, so a step
+// moves about 150 KB through shared memory (1 200 clocks at 128 bytes per clock) for 640 clocks of tensor
+// work; a step takes 1 700 clocks; and every CTA spends about 14 000 clocks outside its steps (6 000
+// until the first products have data, and the last dQ blocks leave after the compute warps are done).
 //
 // One CTA per 128 keys of one (batch, head), one CTA per SM (all 512 columns of tensor memory).
 // It walks the query blocks at or after its keys, 64 queries per step, everything transposed
@@ -13,18 +21,21 @@
 //   dQ   = dS K for two steps (128 queries)  -> its own tensor-memory buffer per pair of steps; the
 //          dS^T tile is read once as the K-major A operand of dK and once as the MN-major A operand
 //          of dQ: the same bytes serve both.
-// Two groups of eight compute warps take alternate steps, so one group's exponentials overlap the
-// other's dS arithmetic and the tensor pipe's work on the neighbouring steps; four more warps only
-// move finished dQ blocks out of tensor memory.  Registers are redistributed (setmaxnreg): 88 per
-// compute thread, 40 for the TMA and MMA warps, the launch count (80) for the drain warps.
+// One thread issues every load (tiles by TMA, the 64 queries' lse and delta by bulk copies from rows a
+// small kernel has prepared), so no load latency sits between two steps.  Two groups of eight compute
+// warps take alternate steps, so one group's exponentials overlap the other's dS arithmetic and the
+// tensor pipe's work on the neighbouring steps; four more warps only move finished dQ blocks out of
+// tensor memory.  Registers are redistributed (setmaxnreg): 88 per compute thread, 40 for the TMA and
+// MMA warps, the launch count (80) for the drain warps.
 //
 // dQ of a 128-query block gets a contribution from every key tile at or before it.  The
 // contributions are added in global memory in key-tile order: tile t waits (bounded) until a counter
-// says tiles 0..t-1 have added theirs, reads the FP32 running sum, adds, writes back and advances the
-// counter; the tile on the diagonal is the last one and writes the BF16 result instead.  The order is
-// fixed, so the result is the same bits on every run.  A CTA only ever waits for a CTA with a lower
-// block index, which the hardware has dispatched before it and which waits only for still lower
-// ones, so the wait cannot deadlock; it is bounded all the same.
+// says tiles 0..t-1 have added theirs, then hands its block to the copy engine as bulk FP32
+// reductions onto the running sum (tile 0 stores), and advances the counter when they have completed;
+// the tile on the diagonal is the last one, adds the running sum itself and writes the BF16 result.
+// The order is fixed, so the result is the same bits on every run.  A CTA only ever waits for a CTA
+// with a lower block index, which the hardware has dispatched before it and which waits only for
+// still lower ones, so the wait cannot deadlock; it is bounded all the same.
 #include "device_utils.cuh"
 #include "sm100.cuh"
 
@@ -34,7 +45,7 @@ namespace {
 constexpr int KeyTile = 128, HeadSize = 64, Step = 64, Ring = 4;
 constexpr int TileBytes = KeyTile * HeadSize * 2; // 16 KB: K, V, or one step's dS^T tile [128 keys][64 queries]
 constexpr int StepBytes = Step * HeadSize * 2;    // 8 KB: Q_j or dO_j
-// Warps in groups of four (register budgets are set per group of four warps): 0 TMA + statistics, 1 MMA, 2-3 idle;
+// Warps in groups of four (register budgets are set per group of four warps): 0 loads, 1 MMA, 2-3 idle;
 // 4-7 move finished dQ blocks out; 8-23 compute.
 constexpr int FirstDrainWarp = 4, DrainWarps = 4, FirstComputeWarp = 8, ComputeWarps = 16;
 constexpr int Threads = 32 * (FirstComputeWarp + ComputeWarps);
@@ -47,15 +58,15 @@ static_assert(32 * (FirstDrainWarp * (LaunchRegisters - ControlRegisters) + Drai
               "released registers must cover the requested ones");
 constexpr int TmemColumns = 512;
 // K, V | ring of (Q_j, dO_j) | dS^T tiles: 2 pairs of steps x 2 steps | statistics ring | dQ staging | barriers
-constexpr int StagePitch = 68; // floats per staged dQ row (64 + 4): a lane's 16-byte pieces spread over all banks
+constexpr int StagePitch = HeadSize; // floats per staged dQ row; the 16-byte pieces of row r sit at piece ^ (r & 7)
 constexpr int OffsetRing = 2 * TileBytes, OffsetDs = OffsetRing + Ring * 2 * StepBytes, OffsetStats = OffsetDs + 4 * TileBytes,
               OffsetStage = OffsetStats + Ring * 128 * 4, OffsetBarriers = OffsetStage + 128 * StagePitch * 4;
 constexpr int SharedBytes = OffsetBarriers + 512 + 1024;
 
 struct FusedParams {
     bf16 *dqkv;
-    const float *lse, *delta;
-    float *dq_sum;   // [tokens][width] FP32 running sums of dQ between key tiles
+    const float *statistics; // [2][batch * heads][tiles * 128]: lse in base 2, then delta (padded rows)
+    float *dq_sum;   // [batch * heads][tiles * 128 queries][64] FP32 running sums of dQ between key tiles, rows in staging order
     int *dq_count;   // [batch * heads][tiles]: key tiles that have added their share to a 128-query block
     int batch, context, heads, width, tiles;
     float scale, scale_log2;
@@ -79,8 +90,33 @@ __device__ __forceinline__ void copy_async16(uint32_t destination, const void *s
 __device__ __forceinline__ void copy_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void copy_async_wait() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
 __device__ __forceinline__ void prefetch_l2(const void *p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
-__device__ __forceinline__ void add_relaxed(int *p, int v) {
-    asm volatile("red.relaxed.gpu.global.add.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+// Adds to a counter; everything the calling thread has observed as done is visible to whoever acquires the new value.
+__device__ __forceinline__ void add_release(int *p, int v) {
+    asm volatile("red.release.gpu.global.add.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+// Bulk operations of the copy engine on one contiguous piece of shared memory (16-byte aligned, a multiple of
+// 16 bytes): a store to global memory, and an FP32 add onto global memory performed in L2.  bulk_wait() returns
+// when all of the calling thread's committed operations are complete.
+__device__ __forceinline__ void bulk_store(void *global, uint32_t shared, uint32_t bytes) {
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(global), "r"(shared), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bulk_add(float *global, uint32_t shared, uint32_t bytes) {
+    asm volatile("cp.reduce.async.bulk.global.shared::cta.bulk_group.add.f32 [%0], [%1], %2;" ::"l"(global), "r"(shared), "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// Returns when at most `Pending` of the calling thread's most recent groups are still incomplete ...
+template <int Pending> __device__ __forceinline__ void bulk_wait() {
+    asm volatile("cp.async.bulk.wait_group %0;" ::"n"(Pending) : "memory");
+}
+// ... and when all of them have at least read their shared memory.
+__device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+// Contiguous global memory -> shared memory by the copy engine (16-byte aligned, a multiple of 16 bytes); the bytes
+// count towards the barrier's phase like those of a tile load.
+__device__ __forceinline__ void bulk_load(uint32_t shared, const void *global, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(shared), "l"(global),
+                 "r"(bytes), "r"(bar)
+                 : "memory");
 }
 // Register budget of the calling group of four warps from here on (all four execute it together).
 template <int Registers> __device__ __forceinline__ void shrink_registers() {
@@ -93,17 +129,6 @@ __device__ __forceinline__ void store_shared16(uint32_t address, uint32_t a, uin
     asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(address), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
 
-#ifdef TG_TRACE
-__device__ long long g_trace[3 * 8 * 64 * 8];
-#define TRACE(role, j, k)                                                                                   \
-    do {                                                                                                    \
-        const int cta_ = blockIdx.x == 100 ? 0 : blockIdx.x == 900 ? 1 : blockIdx.x == 2500 ? 2 : -1;       \
-        if (cta_ >= 0 && (j) < 64)                                                                          \
-            g_trace[((cta_ * 8 + (role)) * 64 + (j)) * 8 + (k)] = clock64();                                \
-    } while (0)
-#else
-#define TRACE(role, j, k)
-#endif
 
 __global__ void __launch_bounds__(Threads, 1)
 flash_backward_kernel(const __grid_constant__ CUtensorMap map_qkv128, const __grid_constant__ CUtensorMap map_qkv64,
@@ -116,8 +141,8 @@ flash_backward_kernel(const __grid_constant__ CUtensorMap map_qkv128, const __gr
     const uint32_t kv_full = smem_address(barriers), qdo_full0 = kv_full + 8, qdo_empty0 = qdo_full0 + 8 * Ring,
                    s_full0 = qdo_empty0 + 8 * Ring, dp_full0 = s_full0 + 16, p_full0 = dp_full0 + 16,
                    ds_full0 = p_full0 + 16, ds_free0 = ds_full0 + 16, dq_full0 = ds_free0 + 16, dq_free0 = dq_full0 + 16,
-                   acc_done = dq_free0 + 16, stored0 = acc_done + 8; // 1 + 2 Ring + 7 x 2 + 1 + 2 = 26 barriers
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(barriers + 26);
+                   acc_done = dq_free0 + 16; // 1 + 2 Ring + 7 x 2 + 1 = 24 barriers
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(barriers + 24);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
     const uint32_t smem_k = base, smem_v = base + TileBytes, smem_qdo = base + OffsetRing, smem_ds = base + OffsetDs;
 
@@ -131,6 +156,11 @@ flash_backward_kernel(const __grid_constant__ CUtensorMap map_qkv128, const __gr
     const int supers = blocks / 2;
 
     grid_launch_dependents(); // the next kernel may set itself up while this one runs
+    if (threadIdx.x == 32) {
+        prefetch_map(&map_qkv128);
+        prefetch_map(&map_qkv64);
+        prefetch_map(&map_do64);
+    }
     if (threadIdx.x == 0) {
         mbarrier_init(kv_full, 1);
         for (int s = 0; s < Ring; ++s) {
@@ -145,7 +175,6 @@ flash_backward_kernel(const __grid_constant__ CUtensorMap map_qkv128, const __gr
             mbarrier_init(ds_free0 + 8 * s, 1);
             mbarrier_init(dq_full0 + 8 * s, 1);
             mbarrier_init(dq_free0 + 8 * s, DrainWarps);
-            mbarrier_init(stored0 + 8 * s, DrainWarps);
         }
         mbarrier_init(acc_done, 1);
         *abort_flag = 0;
@@ -167,58 +196,27 @@ flash_backward_kernel(const __grid_constant__ CUtensorMap map_qkv128, const __gr
     if (warp < FirstDrainWarp) {
       shrink_registers<ControlRegisters>(); // one instruction for the whole group of four warps
       if (warp == 0) {
-        // The whole warp runs the producer loop: lane 0 issues the TMA loads, every lane fetches two
-        // queries' statistics into the ring slot before lane 0's arrival releases them.
+        // The producer: one thread issues every load, tiles and statistics alike, so nothing passes through
+        // its registers and no load latency sits between two steps.
         if (lane == 0) {
             mbarrier_expect_tx(kv_full, 2 * TileBytes);
             tma_load_3d(smem_k, &map_qkv128, p.width + h * HeadSize, row0 + tile * KeyTile, 0, kv_full);
             tma_load_3d(smem_v, &map_qkv128, 2 * p.width + h * HeadSize, row0 + tile * KeyTile, 0, kv_full);
-        }
-        const float *lse = p.lse + (int64_t(b) * p.heads + h) * p.context;
-        const float *delta = p.delta + (int64_t(b) * p.heads + h) * p.context;
-        auto fetch = [&](int j, float (&values)[4]) { // lse (base 2) and delta of queries q0 + lane and q0 + 32 + lane
-            const int q0 = (first_block + j) * Step;
-#pragma unroll
-            for (int u = 0; u < 2; ++u) {
-                const bool inside = j < blocks && q0 + u * 32 + lane < p.context;
-                values[u] = inside ? lse[q0 + u * 32 + lane] * 1.4426950408889634f : 0.f;
-                values[2 + u] = inside ? delta[q0 + u * 32 + lane] : 0.f;
-            }
-        };
-        bool ok = true;
-        auto step = [&](int j, const float (&values)[4]) {
-            const int ring = j % Ring, q0 = (first_block + j) * Step;
-            if (lane == 0) TRACE(0, j, 0);
-            ok = mbarrier_wait(qdo_empty0 + 8 * ring, ((j / Ring) & 1) ^ 1, abort_flag, p.counters, 341);
-            ok = __all_sync(0xffffffffu, ok);
-            if (!ok)
-                return;
-            if (lane == 0) TRACE(0, j, 1);
-#pragma unroll
-            for (int u = 0; u < 2; ++u) {
-                statistics[ring * 128 + u * 32 + lane] = values[u];
-                statistics[ring * 128 + 64 + u * 32 + lane] = values[2 + u];
-            }
-            __syncwarp();
-            if (lane == 0) {
-                const uint32_t bar = qdo_full0 + 8 * ring, dst = smem_qdo + ring * 2 * StepBytes;
-                mbarrier_expect_tx(bar, 2 * StepBytes);
+            const int64_t padded = int64_t(p.tiles) * KeyTile;
+            const float *lse2 = p.statistics + bh * padded, *delta = lse2 + pairs * padded;
+            for (int j = 0; j < blocks; ++j) {
+                const int ring = j % Ring, q0 = (first_block + j) * Step;
+                if (!mbarrier_wait(qdo_empty0 + 8 * ring, ((j / Ring) & 1) ^ 1, abort_flag, p.counters, 341))
+                    break;
+                const uint32_t bar = qdo_full0 + 8 * ring, dst = smem_qdo + ring * 2 * StepBytes,
+                               stats = smem_address(statistics + ring * 128);
+                mbarrier_expect_tx(bar, 2 * StepBytes + 2 * Step * 4);
                 // rows past the end of the tensor arrive as zeros; rows of the next sequence are masked by the compute warps
                 tma_load_3d(dst, &map_qkv64, h * HeadSize, row0 + q0, 0, bar);
                 tma_load_3d(dst + StepBytes, &map_do64, h * HeadSize, row0 + q0, 0, bar);
+                bulk_load(stats, lse2 + q0, Step * 4, bar);
+                bulk_load(stats + Step * 4, delta + q0, Step * 4, bar);
             }
-        };
-        // Two register sets, refilled two steps ahead of their use: the loop never waits for a load it has
-        // just issued (blocks is even).
-        float even[4], odd[4];
-        fetch(0, even);
-        fetch(1, odd);
-        for (int j = 0; j < blocks && ok; j += 2) {
-            step(j, even);
-            fetch(j + 2, even);
-            if (ok)
-                step(j + 1, odd);
-            fetch(j + 3, odd);
         }
       } else if (warp == 1) {
         if (elect_one()) {
@@ -261,12 +259,10 @@ flash_backward_kernel(const __grid_constant__ CUtensorMap map_qkv128, const __gr
             for (int j = 0; j < blocks && ok; ++j) {
                 const int ring = j % Ring, buffer = j & 1, super = j >> 1;
                 const uint64_t q_mn = descriptor_at(qdo_mn_desc, ring * 2 * StepBytes), do_mn = descriptor_at(q_mn, StepBytes);
-                TRACE(1, j, 0);
                 ok = mbarrier_wait(p_full0 + 8 * buffer, (j >> 1) & 1, abort_flag, p.counters, 344);
                 if (!ok)
                     break;
                 tcgen05_fence_after();
-                TRACE(1, j, 1);
 #pragma unroll
                 for (int ks = 0; ks < Step / 16; ++ks) // dV += P^T dO_j: 16 queries = 8 packed columns at (ks / 2) 32 + (ks % 2) 8
                     tcgen05_mma_bf16_ts(tmem_dv, tmem_st + 64 * buffer + (ks / 2) * 32 + (ks % 2) * 8,
@@ -275,12 +271,10 @@ flash_backward_kernel(const __grid_constant__ CUtensorMap map_qkv128, const __gr
                     issue_s(j + 2); // into the buffer whose P^T the products above have just read
                 if (!ok)
                     break;
-                TRACE(1, j, 2);
                 ok = mbarrier_wait(ds_full0 + 8 * buffer, (j >> 1) & 1, abort_flag, p.counters, 345);
                 if (!ok)
                     break;
                 tcgen05_fence_after();
-                TRACE(1, j, 3);
                 const uint64_t ds_tile = descriptor_at(ds_desc, ((super & 1) * 2 + buffer) * TileBytes);
 #pragma unroll
                 for (int ks = 0; ks < Step / 16; ++ks) // dK += dS^T Q_j
@@ -289,7 +283,6 @@ flash_backward_kernel(const __grid_constant__ CUtensorMap map_qkv128, const __gr
                 tcgen05_commit(qdo_empty0 + 8 * ring); // Q_j and dO_j are no longer read
                 if (j + 2 < blocks)
                     issue_dp(j + 2); // the compute warps have read dP^T of step j (they wrote its dS^T)
-                TRACE(1, j, 4);
                 if (buffer == 1) {
                     // dQ of the pair of steps: (dS^T)^T [128 queries x 128 keys] K [128 keys x 64]
                     if (super >= 2) {
@@ -305,58 +298,41 @@ flash_backward_kernel(const __grid_constant__ CUtensorMap map_qkv128, const __gr
                                          descriptor_at(k_mn_desc, ks * 2048), idesc_dq, ks > 0);
                     tcgen05_commit(dq_full0 + 8 * (super & 1));
                     tcgen05_commit(ds_free0 + 8 * (super & 1)); // both dS^T tiles of the pair may be overwritten
-                    TRACE(1, j, 5);
                 }
             }
             if (ok)
                 tcgen05_commit(acc_done);
         }
-      } else if (warp == 2) {
-        // Advances the counter of every block the drain warps have added to: their stores are ordered before
-        // this warp's device-wide fence by the barrier they arrive on, so the slow fence is off their path.
-        // (Warp 3 only completes the group of four.)
-        if (lane == 0) {
-            for (int super = 0; super < supers; ++super) {
-                if (!mbarrier_wait(stored0 + 8 * (super & 1), (super >> 1) & 1, abort_flag, p.counters, 354))
-                    break;
-                if (super == 0)
-                    continue; // the diagonal block is final: nobody waits for it
-                __threadfence();
-                add_relaxed(p.dq_count + int64_t(bh) * p.tiles + tile + super, DrainWarps);
-            }
-        }
       }
     } else if (warp < FirstComputeWarp) {
-        // Four drain warps, one per 32-lane quarter of tensor memory, add this key tile's dQ of every pair of
-        // steps to the running sum in global memory, after the tiles before it; the diagonal tile comes last
-        // and writes the BF16 result.  They run beside the compute warps, so the global round trips (counter,
-        // running sum, fence) are off the critical path: the running sums are requested before the block is
-        // complete in tensor memory, and the counter of a block is advanced after the next block's requests.
-        // A block leaves tensor memory with one query row per lane; it is turned through shared memory so that
-        // every global access of a warp covers two whole 256-byte rows (lane = row parity x 16-byte piece)
-        // instead of 32 different lines: scattered accesses were measured to stall the whole SM's
-        // load/store path, shared-memory traffic of the compute warps included.
+        // Four drain warps, one per 32-lane quarter of tensor memory, move this key tile's dQ of every pair of
+        // steps out, beside the compute warps.  A block leaves tensor memory with one query row per lane and is
+        // staged in shared memory, 256 bytes per row.  For every block but the diagonal one, each lane then hands
+        // its row to the copy engine as one bulk reduction (FP32 add, performed in L2) onto the running sum in
+        // global memory, or a bulk store when this is key tile 0: no load of the running sum, no register
+        // traffic, and the round trips (counter, completion, release) overlap the next block's steps, because
+        // the counter is read before the block is complete in tensor memory and advanced only when the next
+        // block has arrived.  The diagonal block is the last contribution to its queries: the running sum is
+        // copied into the staging rows at the start of the CTA, added in place, and written as BF16, every
+        // global access of a warp covering two whole 256-byte rows (lane = row parity x 16-byte piece); a
+        // lane-per-row pattern there was measured to stall the SM's whole load/store path, the compute
+        // warps' shared-memory traffic included.
         const int quarter = warp % 4;
         const uint32_t lanes = uint32_t(quarter * 32) << 16;
         float *stage = reinterpret_cast<float *>(aligned + OffsetStage) + quarter * 32 * StagePitch; // this warp's 32 rows
         const int piece = lane % 16, parity = lane / 16;
         const bool first = tile == 0;
-        const int row_pitch = p.width / 2; // float4 elements between rows 2 k + parity and 2 (k + 1) + parity
+        // this warp's 32 rows (8 KB) of block tile + s, contiguous, in the staging rows' own order
+        auto sums_of = [&](int s) { return p.dq_sum + ((int64_t(bh) * p.tiles + tile + s) * 128 + quarter * 32) * HeadSize; };
+        int *count = p.dq_count + int64_t(bh) * p.tiles + tile; // count[s]: drain warps of earlier tiles done with block tile + s
         bool ok = true;
-        // Running sums of block `super`, rows 2 k + parity, as float4 pointers; and their copy into the staging
-        // rows, asynchronous (no registers, no wait): issued a whole block ahead of its use.
-        auto sums_of = [&](int super) {
-            return reinterpret_cast<float4 *>(p.dq_sum + (int64_t(row0) + (tile + super) * 128 + quarter * 32 + parity) * p.width +
-                                              h * HeadSize) + piece;
-        };
         auto wait_for_tiles_before = [&](int super, int seen) { // `seen`: lane 0's earlier look; bounded; false when it gave up
             seen = __shfl_sync(0xffffffffu, seen, 0);
             if (seen >= DrainWarps * tile)
                 return true;
             if (lane == 0) {
-                const int *count = p.dq_count + int64_t(bh) * p.tiles + tile + super;
                 const unsigned long long start = global_timer();
-                while ((seen = load_acquire(count)) < DrainWarps * tile) {
+                while ((seen = load_acquire(count + super)) < DrainWarps * tile) {
                     if (*abort_flag)
                         break;
                     if (global_timer() - start > WaitLimitNs) {
@@ -370,88 +346,99 @@ flash_backward_kernel(const __grid_constant__ CUtensorMap map_qkv128, const __gr
             }
             return __shfl_sync(0xffffffffu, seen, 0) >= DrainWarps * tile;
         };
-        auto fetch_sums = [&](int super) {
-            const float4 *source = sums_of(super);
-            const int position0 = (tile + super) * 128 + quarter * 32;
-#pragma unroll
-            for (int k = 0; k < 16; ++k)
-                if (position0 + 2 * k + parity < p.context)
-                    copy_async16(smem_address(stage + (2 * k + parity) * StagePitch + piece * 4), source + k * row_pitch);
-            copy_async_commit();
-        };
-        if (!first) {
+        if (!first) { // the diagonal block's running sum, asynchronously into the staging rows
             ok = wait_for_tiles_before(0, 0);
-            if (ok)
-                fetch_sums(0);
+            if (ok) {
+                const float4 *source = reinterpret_cast<const float4 *>(sums_of(0)) + lane;
+#pragma unroll
+                for (int k = 0; k < 16; ++k) // 8 KB as it lies: 512 bytes per instruction
+                    copy_async16(smem_address(stage) + (lane + 32 * k) * 16, source + 32 * k);
+                copy_async_commit();
+            }
         }
+        int released = 0; // blocks 1..released have had their counters advanced (the diagonal block has none)
         for (int super = 0; super < supers && ok; ++super) {
             const int sb = super & 1;
             const int position0 = (tile + super) * 128 + quarter * 32; // query of this warp's first row
-            const bool last = super == 0, more = super + 1 < supers;
-            int seen_next = 0; // the next block's counter, read now, looked at when this block is done
-            if (!first && more) {
-                if (lane == 0)
-                    seen_next = load_acquire(p.dq_count + int64_t(bh) * p.tiles + tile + super + 1);
-                const float4 *next = sums_of(super + 1);
-#pragma unroll
-                for (int k = 0; k < 16; ++k) // towards L2, for the copy issued at the end of this block
-                    if (position0 + 128 + 2 * k + parity < p.context)
-                        prefetch_l2(next + k * row_pitch);
+            const bool last = super == 0;
+            int seen = 0; // this block's counter, read now, looked at when the block has been staged
+            if (!first && !last && lane == 0)
+                seen = load_acquire(count + super);
+            if (!first && super + 1 < supers) { // the reduction after this one finds its lines in L2: 32 x 256 bytes
+                const char *next = reinterpret_cast<const char *>(sums_of(super + 1)) + lane * 256;
+                prefetch_l2(next);
+                prefetch_l2(next + 128);
             }
-            if (lane == 0 && warp == FirstDrainWarp) TRACE(4, super, 0);
             ok = mbarrier_wait(dq_full0 + 8 * sb, (super >> 1) & 1, abort_flag, p.counters, 347);
             if (!ok)
                 break;
             tcgen05_fence_after();
-            copy_async_wait();
-            __syncwarp(); // the running sums of this block are in the staging rows, whichever lane copied them
-            if (lane == 0 && warp == FirstDrainWarp) TRACE(4, super, 1);
+            if (last) {
+                copy_async_wait();
+                __syncwarp(); // the running sums are in the staging rows, whichever lane copied them
+            } else {
+                if (lane == 0)
+                    bulk_wait_read(); // the copy engine has read the block before from the staging rows
+                __syncwarp();
+            }
+            const bool add = last && !first;
 #pragma unroll 1
-            for (int part = 0; part < 4; ++part) { // 16 columns at a time: tensor memory (+ running sum) -> staging, lane = row
-                uint32_t raw[16];
-                tmem_load_32x16_async(tmem_dq + 64 * sb + lanes + part * 16, raw);
+            for (int part = 0; part < 2; ++part) { // 32 columns at a time: tensor memory -> staging, lane = row
+                uint32_t raw[32];
+                tmem_load_32x32_async(tmem_dq + 64 * sb + lanes + part * 32, raw);
                 tmem_wait_load(raw);
-                float4 *cell = reinterpret_cast<float4 *>(stage + lane * StagePitch + part * 16);
+                float4 *row = reinterpret_cast<float4 *>(stage + lane * StagePitch);
 #pragma unroll
-                for (int g = 0; g < 4; ++g) {
+                for (int g = 0; g < 8; ++g) {
+                    float4 *cell = row + ((part * 8 + g) ^ (lane & 7)); // eight neighbouring rows use eight different banks
                     float4 v = make_float4(__uint_as_float(raw[4 * g]), __uint_as_float(raw[4 * g + 1]),
                                            __uint_as_float(raw[4 * g + 2]), __uint_as_float(raw[4 * g + 3]));
-                    if (!first) {
-                        const float4 o = cell[g];
+                    if (add) {
+                        const float4 o = *cell;
                         v.x += o.x, v.y += o.y, v.z += o.z, v.w += o.w;
                     }
-                    cell[g] = v;
+                    *cell = v;
                 }
             }
             tcgen05_fence_before();
-            __syncwarp(); // the block has left tensor memory and its new sums are complete in the staging rows
+            __syncwarp(); // the block has left tensor memory and is complete in the staging rows
             if (lane == 0)
                 mbarrier_arrive(dq_free0 + 8 * sb);
-            if (lane == 0 && warp == FirstDrainWarp) TRACE(4, super, 2);
-            float4 *target = sums_of(super);
+            if (last) {
 #pragma unroll
-            for (int k = 0; k < 16; ++k) { // out in whole 256-byte rows: lane = row parity x 16-byte piece
-                const int r = 2 * k + parity, position = position0 + r;
-                if (position >= p.context)
-                    continue;
-                const float4 v = *reinterpret_cast<const float4 *>(stage + r * StagePitch + piece * 4);
-                if (last) {
+                for (int k = 0; k < 16; ++k) { // out in whole rows: lane = row parity x 16-byte piece
+                    const int r = 2 * k + parity, position = position0 + r;
+                    if (position >= p.context)
+                        continue;
+                    const float4 v = *reinterpret_cast<const float4 *>(stage + r * StagePitch + (piece ^ (r & 7)) * 4);
                     bf16 *out = p.dqkv + (int64_t(row0) + position) * 3 * p.width + h * HeadSize + piece * 4;
                     *reinterpret_cast<uint2 *>(out) =
                         make_uint2(pack_bf16(v.x * p.scale, v.y * p.scale), pack_bf16(v.z * p.scale, v.w * p.scale));
-                } else {
-                    __stcg(target + k * row_pitch, v);
+                }
+                __syncwarp(); // every lane has read the staging rows before any lane stages the next block
+            } else {
+                fence_async_proxy(); // the copy engine reads what this lane has staged
+                if (!first)
+                    ok = wait_for_tiles_before(super, seen);
+                if (!ok)
+                    break;
+                __syncwarp();
+                if (lane == 0) { // one operation for the warp's 32 rows; rows past the end of the sequence are zeros
+                    if (first)
+                        bulk_store(sums_of(super), smem_address(stage), 32 * HeadSize * 4);
+                    else
+                        bulk_add(sums_of(super), smem_address(stage), 32 * HeadSize * 4);
+                    bulk_commit();
+                    bulk_wait<2>(); // two blocks' time for an operation to complete before its counter is advanced
+                    while (released < super - 2)
+                        add_release(count + ++released, 1);
                 }
             }
-            __syncwarp(); // every lane has read the staging rows (and issued its stores) before lane 0 goes on
-            if (lane == 0)
-                mbarrier_arrive(stored0 + 8 * sb); // warp 2 makes the sums visible and advances the counter
-            if (lane == 0 && warp == FirstDrainWarp) TRACE(4, super, 3);
-            if (!first && more) {
-                ok = wait_for_tiles_before(super + 1, seen_next);
-                if (ok)
-                    fetch_sums(super + 1);
-            }
+        }
+        if (lane == 0) {
+            bulk_wait<0>();
+            while (ok && released < supers - 1)
+                add_release(count + ++released, 1);
         }
     } else {
         grow_registers<ComputeRegisters>();
@@ -466,13 +453,11 @@ flash_backward_kernel(const __grid_constant__ CUtensorMap map_qkv128, const __gr
 
         for (int j = group; j < blocks && ok; j += 2) {
             const int ring = j % Ring, super = j >> 1, use = j >> 1;
-            if (lane == 0 && (warp == FirstComputeWarp || warp == FirstComputeWarp + 8)) TRACE(2 + group, j, 0);
             ok = mbarrier_wait(qdo_full0 + 8 * ring, (j / Ring) & 1, abort_flag, p.counters, 349) && // statistics
                  mbarrier_wait(s_full0 + 8 * group, use & 1, abort_flag, p.counters, 350);
             if (!ok)
                 break;
             tcgen05_fence_after();
-            if (lane == 0 && (warp == FirstComputeWarp || warp == FirstComputeWarp + 8)) TRACE(2 + group, j, 1);
             const float *l2 = statistics + ring * 128 + half * 32, *dl = l2 + 64;
             const int qa = (first_block + j) * Step + half * 32;             // first query of this warp's columns
             const bool none = qa + 31 < warp_first || qa >= p.context;       // every query lies before every key of the warp, or past the end
@@ -505,14 +490,12 @@ flash_backward_kernel(const __grid_constant__ CUtensorMap map_qkv128, const __gr
                 if (lane == 0)
                     mbarrier_arrive(p_full0 + 8 * group);
             }
-            if (lane == 0 && (warp == FirstComputeWarp || warp == FirstComputeWarp + 8)) TRACE(2 + group, j, 2);
             ok = mbarrier_wait(dp_full0 + 8 * group, use & 1, abort_flag, p.counters, 351);
             if (ok && super >= 2) // the dS^T tiles of this pair of steps were last read by the products of pair super - 2
                 ok = mbarrier_wait(ds_free0 + 8 * (super & 1), ((super >> 1) & 1) ^ 1, abort_flag, p.counters, 352);
             if (!ok)
                 break;
             tcgen05_fence_after();
-            if (lane == 0 && (warp == FirstComputeWarp || warp == FirstComputeWarp + 8)) TRACE(2 + group, j, 3);
             // dS^T of this warp's 32 queries: four 16-byte chunks of the key's 128-byte row (128-byte swizzle)
             const uint32_t ds_row = smem_ds + ((super & 1) * 2 + group) * TileBytes + row * 128;
 #pragma unroll
@@ -541,7 +524,6 @@ flash_backward_kernel(const __grid_constant__ CUtensorMap map_qkv128, const __gr
             __syncwarp();
             if (lane == 0)
                 mbarrier_arrive(ds_full0 + 8 * group);
-            if (lane == 0 && (warp == FirstComputeWarp || warp == FirstComputeWarp + 8)) TRACE(2 + group, j, 4);
         }
         if (ok)
             ok = mbarrier_wait(acc_done, 0, abort_flag, p.counters, 353);
@@ -575,10 +557,12 @@ flash_backward_kernel(const __grid_constant__ CUtensorMap map_qkv128, const __gr
         tmem_dealloc(tmem_base, TmemColumns);
 }
 
-// delta[b, h, t] = sum_d dO[t, h, d] * O[t, h, d]: eight threads per (token, head), 8 elements each.
-__global__ void __launch_bounds__(256) attention_delta_kernel(const bf16 *__restrict__ out, const bf16 *__restrict__ dout,
-                                                              float *__restrict__ delta, int64_t vectors, int context,
-                                                              int heads) {
+// Per (batch, head, query): lse in base 2 and delta = sum_d dO[t, h, d] * O[t, h, d], into rows padded to whole
+// key tiles (the kernel above fetches them 64 at a time).  Eight threads per (token, head), 8 elements each.
+__global__ void __launch_bounds__(256) attention_statistics_kernel(const bf16 *__restrict__ out, const bf16 *__restrict__ dout,
+                                                                   const float *__restrict__ lse, float *__restrict__ statistics,
+                                                                   int64_t vectors, int context, int heads, int64_t padded,
+                                                                   int64_t pairs) {
     const int64_t i = blockIdx.x * int64_t(blockDim.x) + threadIdx.x;
     float sum = 0.f;
     if (i < vectors) {
@@ -594,25 +578,22 @@ __global__ void __launch_bounds__(256) attention_delta_kernel(const bf16 *__rest
     sum += __shfl_xor_sync(0xffffffffu, sum, 1);
     if (i < vectors && (i & 7) == 0) {
         const int64_t pair = i >> 3, token = pair / heads; // (token, head)
-        const int head = int(pair % heads);
-        delta[(token / context * heads + head) * context + token % context] = sum;
+        const int64_t bh = token / context * heads + pair % heads, t = token % context;
+        statistics[bh * padded + t] = lse[bh * context + t] * 1.4426950408889634f;
+        statistics[(pairs + bh) * padded + t] = sum;
     }
 }
 } // namespace
 
-#ifdef TG_TRACE
-extern "C" int tg_debug_trace(long long *out, int count) {
-    return int(cudaMemcpyFromSymbol(out, g_trace, size_t(count) * sizeof(long long)));
-}
-#endif
 
 size_t flash_backward_scratch_bytes(int batch, int context, int heads) {
     const size_t tiles = size_t(context + KeyTile - 1) / KeyTile;
-    return size_t(batch) * context * heads * HeadSize * sizeof(float) + size_t(batch) * heads * tiles * sizeof(int);
+    const size_t pairs = size_t(batch) * heads;
+    // running sums of dQ, statistics (lse and delta, padded rows), counters
+    return pairs * tiles * KeyTile * HeadSize * sizeof(float) + 2 * pairs * tiles * KeyTile * sizeof(float) + pairs * tiles * sizeof(int);
 }
 
-void launch_flash_attention_backward_fused(const void *qkv, const void *out, const void *dout, const float *lse,
-                                           float *delta, void *dqkv, void *scratch, int batch, int context, int heads,
+void launch_flash_attention_backward_fused(const void *qkv, const void *out, const void *dout, const float *lse, void *dqkv, void *scratch, int batch, int context, int heads,
                                            StepCounters *counters, cudaStream_t s) {
     static bool configured[64] = {};
     int device = 0;
@@ -628,19 +609,25 @@ void launch_flash_attention_backward_fused(const void *qkv, const void *out, con
     }
     const int width = heads * HeadSize;
     FusedParams p{};
-    p.dqkv = static_cast<bf16 *>(dqkv), p.lse = lse, p.delta = delta;
+    p.dqkv = static_cast<bf16 *>(dqkv);
     p.batch = batch, p.context = context, p.heads = heads, p.width = width;
     p.tiles = (context + KeyTile - 1) / KeyTile;
+    const size_t pairs = size_t(batch) * heads, padded = size_t(p.tiles) * KeyTile;
     p.dq_sum = static_cast<float *>(scratch);
-    p.dq_count = reinterpret_cast<int *>(p.dq_sum + size_t(batch) * context * width);
+    float *statistics = p.dq_sum + pairs * padded * HeadSize;
+    p.statistics = statistics;
+    p.dq_count = reinterpret_cast<int *>(statistics + 2 * pairs * padded);
     p.scale = 1.f / sqrtf(float(HeadSize));
     p.scale_log2 = 1.4426950408889634f * p.scale;
     p.counters = counters;
     const uint64_t rows = uint64_t(batch) * context;
     const int64_t vectors = int64_t(rows) * width / 8;
-    attention_delta_kernel<<<unsigned((vectors + 255) / 256), 256, 0, s>>>(
-        static_cast<const bf16 *>(out), static_cast<const bf16 *>(dout), delta, vectors, context, heads);
-    CHECK_CUDA(cudaMemsetAsync(p.dq_count, 0, size_t(batch) * heads * p.tiles * sizeof(int), s));
+    if (padded != size_t(context)) // the padding is read (and masked): keep it finite
+        CHECK_CUDA(cudaMemsetAsync(statistics, 0, 2 * pairs * padded * sizeof(float), s));
+    attention_statistics_kernel<<<unsigned((vectors + 255) / 256), 256, 0, s>>>(
+        static_cast<const bf16 *>(out), static_cast<const bf16 *>(dout), lse, statistics, vectors, context, heads, int64_t(padded),
+        int64_t(pairs));
+    CHECK_CUDA(cudaMemsetAsync(p.dq_count, 0, pairs * p.tiles * sizeof(int), s));
     CUtensorMap qkv128 = make_map_bf16(qkv, uint64_t(3) * width, rows, 1, uint64_t(3) * width, 0, HeadSize, 128);
     CUtensorMap qkv64 = make_map_bf16(qkv, uint64_t(3) * width, rows, 1, uint64_t(3) * width, 0, HeadSize, Step);
     CUtensorMap do64 = make_map_bf16(dout, width, rows, 1, width, 0, HeadSize, Step);

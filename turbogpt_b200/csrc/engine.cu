@@ -156,10 +156,6 @@ void Engine::initialize() {
     bytes(dactivated, M * Hd);
     bytes(dqkv, M * 3 * W);
     allocate(attention_scratch, M * c.heads, false);
-#ifndef TG_TWO_KERNEL_ATTENTION_BACKWARD
-    if (c.attention == TG_ATTENTION_SOFTMAX && act == Dtype::BF16 && tensor_cores && flash_attention_supported(W, c.heads))
-        allocate(attention_dq_scratch, flash_backward_scratch_bytes(c.base.batch, T, c.heads), false);
-#endif
     norm_blocks = norm_backward_blocks(tokens, sms);
     allocate(norm_partial, size_t(norm_blocks) * 2 * W, false);
     if (W <= 1024 && tokens >= 4096)
@@ -528,12 +524,8 @@ void Engine::backward() {
             SoftmaxAttentionBackwardArgs at{a.qkv, a.attended, dbranch, a.lse, attention_scratch, dqkv, B, T, W, H};
             run(FAttentionBackward, [&] {
                 if (tensor_cores && act == Dtype::BF16 && flash_attention_supported(W, H)) {
-                    if (attention_dq_scratch)
-                        launch_flash_attention_backward_fused(a.qkv, a.attended, dbranch, a.lse, attention_scratch, dqkv,
-                                                              attention_dq_scratch, B, T, H, counters, stream);
-                    else
-                        launch_flash_attention_backward(a.qkv, a.attended, dbranch, a.lse, attention_scratch, dqkv, B, T,
-                                                        H, counters, stream);
+                    launch_flash_attention_backward(a.qkv, a.attended, dbranch, a.lse, attention_scratch, dqkv, B, T, H,
+                                                    counters, stream);
                 } else {
                     launch_softmax_attention_backward(act, at, stream);
                 }

@@ -74,7 +74,6 @@ struct Engine {
     void *dhidden[2] = {nullptr, nullptr}, *dbranch = nullptr, *dwide = nullptr, *dactivated = nullptr,
          *dqkv = nullptr;
     float *attention_scratch = nullptr; // dt (arg-max) or delta (softmax)
-    uint8_t *attention_dq_scratch = nullptr; // running dQ sums and counters of the fused attention backward
     float *token_losses = nullptr, *loss_history = nullptr, *norm_partial = nullptr, *sumsq_partial = nullptr,
           *logits_fp32 = nullptr, *mean_loss = nullptr, *embedding_partial = nullptr;
     int norm_blocks = 0, sumsq_blocks = 0;

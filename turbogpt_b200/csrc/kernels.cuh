@@ -116,8 +116,7 @@ void launch_flash_attention_backward(const void *qkv, const void *out, const voi
 // `scratch` (flash_backward_scratch_bytes) holds the FP32 running sums of dQ between key tiles and their
 // counters; `delta` as above.
 size_t flash_backward_scratch_bytes(int batch, int context, int heads);
-void launch_flash_attention_backward_fused(const void *qkv, const void *out, const void *dout, const float *lse,
-                                           float *delta, void *dqkv, void *scratch, int batch, int context, int heads,
+void launch_flash_attention_backward_fused(const void *qkv, const void *out, const void *dout, const float *lse, void *dqkv, void *scratch, int batch, int context, int heads,
                                            StepCounters *counters, cudaStream_t s);
 
 // ---- MLP activations (reference cuda/ops.cuh:118-144) ----

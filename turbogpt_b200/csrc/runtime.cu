@@ -3,6 +3,7 @@
 // include/turbogpt_b200.h.  Every function converts exceptions to the error convention:
 // negative int / NULL and a thread-local message.
 #include "engine.h"
+#include <mutex>
 #include <cstring>
 
 static thread_local std::string last_error;
@@ -339,32 +340,48 @@ int tg_ex_attention_forward(const void *qkv, void *out, float *lse, int batch, i
         CHECK_CUDA(cudaGetLastError());
     });
 }
+namespace {
+// Scratch of the stand-alone attention backward call: one grow-only allocation per device, kept until the
+// process ends, so that repeated calls cost no allocator traffic.  Calls on the same device must not overlap.
+void *attention_scratch(size_t bytes) {
+    static std::mutex guard;
+    static void *memory[64] = {};
+    static size_t capacity[64] = {};
+    int device = 0;
+    CHECK_CUDA(cudaGetDevice(&device));
+    if (device >= 64)
+        throw std::runtime_error("device index out of range");
+    std::lock_guard<std::mutex> lock(guard);
+    if (capacity[device] < bytes) {
+        CHECK_CUDA(cudaDeviceSynchronize());
+        if (memory[device])
+            CHECK_CUDA(cudaFree(memory[device]));
+        memory[device] = nullptr, capacity[device] = 0;
+        CHECK_CUDA(cudaMalloc(&memory[device], bytes));
+        capacity[device] = bytes;
+    }
+    return memory[device];
+}
+} // namespace
 int tg_ex_attention_backward(const void *qkv, const void *out, const void *dout, const float *lse, void *dqkv,
                              int batch, int context, int heads, int d_head, int tensor_cores, void *stream) {
     return guarded([&] {
         require_sm100();
         if (tensor_cores && !flash_attention_supported(heads * d_head, heads))
             throw std::runtime_error("tensor-core attention needs a head size of 64");
-        float *delta = nullptr;
-        CHECK_CUDA(cudaMallocAsync(&delta, size_t(batch) * heads * context * sizeof(float),
-                                   static_cast<cudaStream_t>(stream)));
-        SoftmaxAttentionBackwardArgs a{qkv, out, dout, lse, delta, dqkv, batch, context, heads * d_head, heads};
-        if (tensor_cores) {
-#ifndef TG_TWO_KERNEL_ATTENTION_BACKWARD
-            void *scratch = nullptr;
-            CHECK_CUDA(cudaMallocAsync(&scratch, flash_backward_scratch_bytes(batch, context, heads),
-                                       static_cast<cudaStream_t>(stream)));
-            launch_flash_attention_backward_fused(qkv, out, dout, lse, delta, dqkv, scratch, batch, context, heads,
-                                                  nullptr, static_cast<cudaStream_t>(stream));
-            CHECK_CUDA(cudaFreeAsync(scratch, static_cast<cudaStream_t>(stream)));
-#else
-            launch_flash_attention_backward(qkv, out, dout, lse, delta, dqkv, batch, context, heads, nullptr,
-                                            static_cast<cudaStream_t>(stream));
-#endif
+        cudaStream_t s = static_cast<cudaStream_t>(stream);
+        if (tensor_cores == TG_ATTENTION_BACKWARD_SINGLE_PASS) {
+            launch_flash_attention_backward_fused(qkv, out, dout, lse, dqkv,
+                                                  attention_scratch(flash_backward_scratch_bytes(batch, context, heads)), batch,
+                                                  context, heads, nullptr, s);
+        } else if (tensor_cores) { // what the engine runs: dQ by query tile, then dK and dV by key tile
+            float *delta = static_cast<float *>(attention_scratch(size_t(batch) * heads * context * sizeof(float)));
+            launch_flash_attention_backward(qkv, out, dout, lse, delta, dqkv, batch, context, heads, nullptr, s);
         } else {
-            launch_softmax_attention_backward(Dtype::BF16, a, static_cast<cudaStream_t>(stream));
+            float *delta = static_cast<float *>(attention_scratch(size_t(batch) * heads * context * sizeof(float)));
+            SoftmaxAttentionBackwardArgs a{qkv, out, dout, lse, delta, dqkv, batch, context, heads * d_head, heads};
+            launch_softmax_attention_backward(Dtype::BF16, a, s);
         }
-        CHECK_CUDA(cudaFreeAsync(delta, static_cast<cudaStream_t>(stream)));
         CHECK_CUDA(cudaGetLastError());
     });
 }

@@ -59,7 +59,7 @@ def gemm_case(lib, m, n, k, layout, iters, out_fp32=False, tensor_cores=True):
             "us": seconds * 1e6, "tflops": 2.0 * m * n * k / seconds / 1e12}
 
 
-def attention_case(lib, batch, context, heads, iters, backward):
+def attention_case(lib, batch, context, heads, iters, backward, form=1):
     d_head, width = 64, heads * 64
     g = torch.Generator(device="cuda").manual_seed(0)
     qkv = torch.randn(batch * context, 3 * width, generator=g, device="cuda").bfloat16()
@@ -76,12 +76,13 @@ def attention_case(lib, batch, context, heads, iters, backward):
 
     def back():
         if lib.tg_ex_attention_backward(qkv.data_ptr(), out.data_ptr(), dout.data_ptr(), lse.data_ptr(),
-                                        dqkv.data_ptr(), batch, context, heads, d_head, 1, None):
+                                        dqkv.data_ptr(), batch, context, heads, d_head, form, None):
             raise RuntimeError(lib.tg_error().decode())
 
     seconds = _time(back if backward else forward, iters)
     flops = 4.0 * batch * heads * context * context * d_head / 2 * (2.5 if backward else 1.0)
-    return {"kernel": "attention_backward" if backward else "attention_forward", "batch": batch, "context": context,
+    name = ("attention_backward" if form == 1 else "attention_backward_single_pass") if backward else "attention_forward"
+    return {"kernel": name, "batch": batch, "context": context,
             "heads": heads, "us": seconds * 1e6, "tflops": flops / seconds / 1e12}
 
 
@@ -222,6 +223,8 @@ def main() -> None:
     parser.add_argument("--shape", default="")
     parser.add_argument("--layout", default="")
     parser.add_argument("--iters", type=int, default=20)
+    parser.add_argument("--batch", type=int, default=32, help="sequences of the attention cases")
+    parser.add_argument("--context", type=int, default=1024, help="tokens per sequence of the attention cases")
     args = parser.parse_args()
     lib = bridge.load_library()
     results = []
@@ -239,9 +242,11 @@ def main() -> None:
         for m, n, k, layout in cases:
             results.append(gemm_case(lib, m, n, k, layout, args.iters, out_fp32=layout == "mm"))
     if args.only in ("all", "attention", "attention_forward"):
-        results.append(attention_case(lib, 32, 1024, 12, args.iters, False))
+        results.append(attention_case(lib, args.batch, args.context, 12, args.iters, False))
     if args.only in ("all", "attention", "attention_backward"):
-        results.append(attention_case(lib, 32, 1024, 12, args.iters, True))
+        results.append(attention_case(lib, args.batch, args.context, 12, args.iters, True))
+    if args.only in ("attention", "attention_backward_single_pass"):
+        results.append(attention_case(lib, args.batch, args.context, 12, args.iters, True, form=2))
     if args.only in ("all", "cross_entropy"):
         results.append(cross_entropy_case(lib, tokens, args.iters))
     if args.only in ("all", "norm", "norm_forward"):
