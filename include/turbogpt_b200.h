@@ -235,6 +235,11 @@ int tg_ex_norm_backward(int kind, const void *x, const void *dy, const void *sca
  * = (softmax - onehot) * scale, written in place over logits when dlogits == logits. */
 int tg_ex_cross_entropy(const void *logits, const uint8_t *targets, float *losses, void *dlogits, int rows,
                         float scale, void *stream);
+/* The language-model head and its loss in one tensor-core kernel, as a training step runs them
+ * (cuda/model.cuh:31-58): logits = x[rows, width] head[256, width]^T stay in FP32 inside the kernel;
+ * losses[rows] floats; dlogits BF16 [rows, 256] = (softmax - onehot) * scale, or NULL for the loss alone. */
+int tg_ex_head_cross_entropy(const void *x, const void *head, const uint8_t *targets, float *losses, void *dlogits,
+                             int rows, int width, float scale, void *stream);
 
 #ifdef __cplusplus
 }

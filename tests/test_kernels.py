@@ -82,6 +82,34 @@ def test_cross_entropy_matches_torch():
     assert max_relative(grads.float().cpu().numpy(), (probs * scale).numpy()) <= 4e-3
 
 
+@pytest.mark.parametrize("rows,width", [(4096 + 3, 768), (300, 256), (33000, 768), (128, 64)])
+def test_head_and_cross_entropy_in_one_kernel(rows, width):
+    """The training step's head: logits stay in FP32 inside the kernel (cuda/model.cuh:31-58)."""
+    lib = load_library()
+    g = torch.Generator(device="cuda").manual_seed(0)
+    x = torch.randn(rows, width, generator=g, device="cuda").bfloat16()
+    head = (torch.randn(256, width, generator=g, device="cuda") * (4.0 / width ** 0.5)).bfloat16()
+    targets = torch.randint(0, 256, (rows,), generator=g, device="cuda").to(torch.uint8)
+    losses = torch.empty(rows, device="cuda")
+    grads = torch.empty(rows, 256, device="cuda", dtype=torch.bfloat16)
+    scale = 1.0 / rows
+    assert lib.tg_ex_head_cross_entropy(x.data_ptr(), head.data_ptr(), targets.data_ptr(), losses.data_ptr(),
+                                        grads.data_ptr(), rows, width, scale, None) == 0, lib.tg_error()
+    torch.cuda.synchronize()
+    logits = x.double() @ head.double().T
+    expected = torch.nn.functional.cross_entropy(logits, targets.long(), reduction="none")
+    probabilities = torch.softmax(logits, -1)
+    probabilities[torch.arange(rows), targets.long()] -= 1
+    torch.testing.assert_close(losses.double(), expected, rtol=2e-5, atol=2e-5)
+    assert max_relative(grads.float().cpu().numpy(), (probabilities * scale).float().cpu().numpy()) <= 4e-3
+    # the loss alone (evaluation), and the same bits on a second call
+    again = torch.empty_like(losses)
+    assert lib.tg_ex_head_cross_entropy(x.data_ptr(), head.data_ptr(), targets.data_ptr(), again.data_ptr(), None,
+                                        rows, width, scale, None) == 0, lib.tg_error()
+    torch.cuda.synchronize()
+    assert torch.equal(again, losses)
+
+
 @pytest.mark.parametrize("batch,context,heads,d_head", [(2, 128, 2, 64), (1, 200, 3, 64), (2, 64, 2, 32),
                                                         (2, 1024, 2, 64), (3, 520, 1, 64), (1, 8, 1, 64),
                                                         (2, 40, 2, 64), (1, 65, 1, 64)])

@@ -182,6 +182,7 @@ def load_library() -> C.CDLL:
     lib.tg_ex_norm_forward.argtypes = [I, P, P, P, P, P, P, P, I, I, P]
     lib.tg_ex_norm_backward.argtypes = [I, P, P, P, P, P, P, P, P, P, I, I, P]
     lib.tg_ex_cross_entropy.argtypes = [P, P, P, P, I, C.c_float, P]
+    lib.tg_ex_head_cross_entropy.argtypes = [P, P, P, P, P, I, I, C.c_float, P]
     _library = lib
     return lib
 
@@ -191,7 +192,7 @@ EXPORTS = ('error create destroy parameter_count blocks shared_bytes set_weights
            'onecycle_point set_onecycle batch predict optimizer_test synchronize').split()
 EXTENSIONS = ('reference_config gpt_config parameter_count parameter_layout initialize_weights config_digest save_checkpoint load_checkpoint nccl_unique_id '
               'stream sample train_mean_loss train_batch profile launch_count read_activation selftest_bounded_wait gemm weight_gradient_static last_device_error attention_forward attention_backward '
-              'norm_forward norm_backward cross_entropy').split()
+              'norm_forward norm_backward cross_entropy head_cross_entropy').split()
 
 
 class Native:

@@ -8,6 +8,8 @@
 #include <cstring>
 #include <dlfcn.h>
 
+constexpr size_t SimtScratchBytes = size_t(6) << 20; // bounds gemm_simt_scratch_bytes for every shape it cuts
+
 const char *const family_names[FamilyCount] = {
     "sample", "embedding", "norm", "gemm_forward", "gemm_input_grad", "gemm_weight_grad", "attention_forward",
     "attention_backward", "activation", "cross_entropy", "norm_backward", "embedding_backward", "optimizer",
@@ -156,6 +158,7 @@ void Engine::initialize() {
     bytes(dactivated, M * Hd);
     bytes(dqkv, M * 3 * W);
     allocate(attention_scratch, M * c.heads, false);
+    allocate(simt_scratch, SimtScratchBytes / sizeof(float), false);
     norm_blocks = norm_backward_blocks(tokens, sms);
     allocate(norm_partial, size_t(norm_blocks) * 2 * W, false);
     if (W <= 1024 && tokens >= 4096)
@@ -294,7 +297,7 @@ void Engine::gemm(Family f, GemmArgs g) {
         if (tensor_cores && gemm_tc_supported(g))
             launch_gemm_tc(g, gemm_sms, counters, stream, &gemm_workspace);
         else
-            launch_gemm_simt(g, stream);
+            launch_gemm_simt(g, stream, gemm_simt_scratch_bytes(g) <= SimtScratchBytes ? simt_scratch : nullptr);
     });
 }
 void Engine::check_device_error() {
@@ -419,9 +422,19 @@ void Engine::forward(bool want_gradient, bool dump_logits) {
     GemmArgs head;
     head.a = final_normed, head.a_row = W, head.b = weight(layout.head), head.b_row = W, head.c = logits;
     head.ldc = Vocabulary, head.m = M, head.n = Vocabulary, head.k = W, head.out = act;
+    const float divisor = float(int64_t(B) * c.world * T);
+    // Training steps take the loss and its gradient from the head product's FP32 accumulators (the reference
+    // fuses them the same way, cuda/model.cuh:31-58); calls that return logits run the two kernels.
+    GemmArgs fused = head;
+    fused.in = act, fused.epilogue = Epilogue::CrossEntropy, fused.r = y, fused.c2 = token_losses;
+    fused.c = want_gradient ? logits : nullptr, fused.alpha = 1.f / divisor;
+    if (tensor_cores && !dump_logits && act == Dtype::BF16 && gemm_tc_supported(fused)) {
+        gemm(FGemmForward, fused);
+        return;
+    }
     gemm(FGemmForward, head);
     CrossEntropyArgs ce{logits, y, token_losses, want_gradient ? logits : nullptr,
-                        dump_logits ? logits_fp32 : nullptr, float(int64_t(B) * c.world * T), M};
+                        dump_logits ? logits_fp32 : nullptr, divisor, M};
     run(FCrossEntropy, [&] { launch_cross_entropy(act, ce, stream); });
 }
 

@@ -103,6 +103,7 @@ struct Engine {
     int64_t family_launches[FamilyCount] = {};
     int64_t launches = 0, graph_launches = 0;
     GemmWorkspace gemm_workspace; // this engine's split-K scratch (never shared with another engine or stream)
+    float *simt_scratch = nullptr; // partial tiles of CUDA-core GEMMs that are cut along K (6 MB bounds every shape)
     cudaGraphExec_t step_graph = nullptr; // one captured training step
     bool graph_warm = false;
     int forward_batch = 0; // sequences the next forward pass covers (0: the configured batch)

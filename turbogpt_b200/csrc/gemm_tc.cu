@@ -37,6 +37,7 @@ constexpr int StageABytes = BM * BK * 2;
 constexpr int EpilogueWarps = 16;
 constexpr int Threads = 64 + 32 * EpilogueWarps; // warp 0: TMA, warp 1: MMA, then the epilogue warps
 constexpr int ControlBytes = 512;   // barriers, TMEM slot, flags
+constexpr int RowScratchBytes = 2 * 4 * BM * 4; // CrossEntropy: row maxima and row sums of the four column shares
 constexpr int MaxShared = 232448 - 1024; // 227 KB less the runtime's own reservation
 constexpr int TmemColumns = 512;
 
@@ -310,6 +311,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         const int quarter = warp % 4, share = (warp - 2) / 4;
         constexpr bool has_r = Kind == int(Epilogue::Residual) || Kind == int(Epilogue::GeluGrad) ||
                                Kind == int(Epilogue::Axpby);
+        constexpr bool whole_rows = Kind == int(Epilogue::CrossEntropy); // the sixteen warps meet per tile
         int buffer = 0;
         uint32_t buffer_phase = 0;
         for (long long w = first_item; w < work_items; w += item_stride) {
@@ -318,7 +320,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             const int nt = int(t % n_tiles), mt = int(t / n_tiles % m_units) * Unit + int(rank),
                       z = int(t / n_tiles / m_units);
             bool ready = mbarrier_wait(tfull0 + 8 * buffer, buffer_phase, abort_flag, p.counters, 104);
-            if (p.splits > 1) // the eight warps meet at named barriers below: leave together or not at all
+            if (p.splits > 1 || whole_rows) // the warps meet at named barriers below: leave together or not at all
                 ready = epilogue_all(ready);
             if (!ready)
                 break;
@@ -327,7 +329,77 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + buffer * MaxBN;
             const int tile_columns = min(p.bn, p.n - nt * p.bn);
             const int chunks = (tile_columns + 31) / 32;
-            if (p.splits == 1) {
+            if constexpr (whole_rows) {
+                // One 256-column tile holds whole rows of logits.  A thread owns row `row` in the 32-column chunks
+                // `share` and `share + 4`; the four shares of a row exchange their maxima and sums through shared
+                // memory and add them in share order.
+                float *row_high = reinterpret_cast<float *>(aligned + p.stages * stage_bytes + ControlBytes);
+                float *row_sum = row_high + Shares * BM;
+                const int local = quarter * 32 + lane;
+                float v[64];
+#pragma unroll
+                for (int half = 0; half < 2; ++half) {
+                    uint32_t acc[32];
+                    tmem_load_32x32_async(taddr + (share + half * Shares) * 32, acc);
+                    tmem_wait_load(acc);
+#pragma unroll
+                    for (int j = 0; j < 32; ++j)
+                        v[half * 32 + j] = __uint_as_float(acc[j]);
+                }
+                tcgen05_fence_before();
+                __syncwarp();
+                if (lane == 0) { // the accumulator is in registers: the next tile's products may overwrite it
+                    if constexpr (Pair)
+                        mbarrier_arrive_cluster(cluster_address(tempty0 + 8 * buffer, 0));
+                    else
+                        mbarrier_arrive(tempty0 + 8 * buffer);
+                }
+                const bool row_ok = row < p.m;
+                const int target = row_ok ? static_cast<const uint8_t *>(p.r)[row] : 0;
+                float high = v[0], picked = 0.f;
+#pragma unroll
+                for (int j = 0; j < 64; ++j) {
+                    high = fmaxf(high, v[j]);
+                    const int column = (share + (j / 32) * Shares) * 32 + j % 32;
+                    picked = column == target ? v[j] : picked;
+                }
+                row_high[share * BM + local] = high;
+                asm volatile("bar.sync 1, 512;" ::: "memory");
+                high = fmaxf(fmaxf(row_high[local], row_high[BM + local]), fmaxf(row_high[2 * BM + local], row_high[3 * BM + local]));
+                float sum = 0.f;
+#pragma unroll
+                for (int j = 0; j < 64; ++j) {
+                    v[j] = expf(v[j] - high);
+                    sum += v[j];
+                }
+                row_sum[share * BM + local] = sum;
+                asm volatile("bar.sync 1, 512;" ::: "memory");
+                sum = ((row_sum[local] + row_sum[BM + local]) + row_sum[2 * BM + local]) + row_sum[3 * BM + local];
+                if (row_ok) {
+                    if (target / 32 % Shares == share)
+                        static_cast<float *>(p.c2)[row] = high + logf(sum) - picked;
+                    if (p.c) {
+                        const float inverse = 1.f / sum;
+#pragma unroll
+                        for (int half = 0; half < 2; ++half) {
+                            const int column = (share + half * Shares) * 32;
+                            char *dst = (char *)p.c + (row * p.ldc + column) * 2;
+#pragma unroll
+                            for (int g = 0; g < 2; ++g) {
+                                uint32_t out[8];
+#pragma unroll
+                                for (int j = 0; j < 8; ++j) {
+                                    const int e = half * 32 + g * 16 + 2 * j;
+                                    const float a = (v[e] * inverse - (column + g * 16 + 2 * j == target ? 1.f : 0.f)) * p.alpha;
+                                    const float b = (v[e + 1] * inverse - (column + g * 16 + 2 * j + 1 == target ? 1.f : 0.f)) * p.alpha;
+                                    out[j] = pack_bf16(a, b);
+                                }
+                                store_global32(dst + g * 32, out, p.wide, true);
+                            }
+                        }
+                    }
+                }
+            } else if (p.splits == 1) {
                 const bool row_ok = row < p.m;
                 const long long c_row = z * p.c_batch + row * p.ldc, r_row = z * p.r_batch + row * p.ldr;
                 auto process = [&](uint32_t (&acc)[32], int c) {
@@ -525,6 +597,7 @@ struct Schedule {
 Schedule choose_schedule(const GemmArgs &g, int sms) {
     const bool b_mn = g.b_col != 1;
     const bool second_tensor = g.epilogue != Epilogue::Store; // K is split only for plain stores
+    const bool whole_rows = g.epilogue == Epilogue::CrossEntropy; // a tile must hold complete rows
     const int m_tiles = (g.m + BM - 1) / BM, k_blocks = (g.k + BK - 1) / BK;
     Schedule best;
     long long best_time = 0;
@@ -536,6 +609,8 @@ Schedule choose_schedule(const GemmArgs &g, int sms) {
         for (int bn : {256, 192, 128, 64}) {
             if (bn > 64 && bn - 64 >= g.n)
                 continue; // a narrower tile already covers N
+            if (whole_rows && bn != 256)
+                continue;
             if (unit == 2 && (bn == 64 || (b_mn && bn == 192)))
                 continue; // each CTA stages bn/2 rows of B: whole 64-row blocks when B is MN-major
             const long long tiles = m_units * ((g.n + bn - 1) / bn) * g.batch;
@@ -621,10 +696,11 @@ void launch_schedule(const GemmArgs &g, const Schedule &sc, int sms, float *part
     const long long tiles = (long long)(padded_m_tiles / unit) * n_tiles * g.batch; // scheduling units
     const int bn_local = p.bn / unit;
     const int stage_bytes = StageABytes + bn_local * BK * 2;
-    p.stages = (MaxShared - 1024 - ControlBytes) / stage_bytes;
+    const int row_scratch = g.epilogue == Epilogue::CrossEntropy ? RowScratchBytes : 0;
+    p.stages = (MaxShared - 1024 - ControlBytes - row_scratch) / stage_bytes;
     if (p.stages > MaxStages)
         p.stages = MaxStages;
-    const int shared = p.stages * stage_bytes + ControlBytes + 1024;
+    const int shared = p.stages * stage_bytes + ControlBytes + row_scratch + 1024;
     p.c = g.c, p.c2 = g.c2, p.r = g.r;
     p.ldc = g.ldc, p.ldr = g.ldr, p.c_batch = g.c_batch, p.r_batch = g.r_batch;
     p.alpha = g.alpha, p.beta = g.beta;
@@ -635,8 +711,9 @@ void launch_schedule(const GemmArgs &g, const Schedule &sc, int sms, float *part
         auto aligned32 = [&](const void *ptr, int64_t ld, int64_t batch_stride) {
             return !ptr || (reinterpret_cast<uintptr_t>(ptr) % 32 == 0 && ld % per32 == 0 && batch_stride % per32 == 0);
         };
-        p.wide = aligned32(g.c, g.ldc, g.c_batch) && aligned32(g.c2, g.ldc, g.c_batch) &&
-                 aligned32(g.r, g.ldr, g.r_batch);
+        p.wide = g.epilogue == Epilogue::CrossEntropy
+                     ? aligned32(g.c, g.ldc, 0)
+                     : aligned32(g.c, g.ldc, g.c_batch) && aligned32(g.c2, g.ldc, g.c_batch) && aligned32(g.r, g.ldr, g.r_batch);
     }
     CUtensorMap map_a = p.a_mn ? make_map_bf16(g.a, g.m, g.k, g.batch, lda, g.a_batch, 64, BK)
                                : make_map_bf16(g.a, g.k, g.m, g.batch, lda, g.a_batch, BK, BM);
@@ -685,6 +762,7 @@ void launch_schedule(const GemmArgs &g, const Schedule &sc, int sms, float *part
             case Epilogue::GeluDual: launch(gemm_tc_kernel<int(Epilogue::GeluDual), false, P>); break;
             case Epilogue::GeluGrad: launch(gemm_tc_kernel<int(Epilogue::GeluGrad), false, P>); break;
             case Epilogue::Axpby: launch(gemm_tc_kernel<int(Epilogue::Axpby), false, P>); break;
+            case Epilogue::CrossEntropy: launch(gemm_tc_kernel<int(Epilogue::CrossEntropy), false, P>); break;
             }
         }
     };
@@ -709,8 +787,11 @@ bool gemm_tc_supported(const GemmArgs &g) {
     const int64_t lda = a_k ? g.a_row : g.a_col, ldb = b_k ? g.b_row : g.b_col;
     if (lda % 8 || ldb % 8 || g.ldc % 8 || (g.r && g.ldr % 8))
         return false;
+    const bool loss = g.epilogue == Epilogue::CrossEntropy; // R holds one byte per row there
+    if (loss && (g.n != 256 || g.batch != 1 || g.out != Dtype::BF16 || !g.r || !g.c2 || g.a_col != 1 || g.b_col != 1))
+        return false;
     if (reinterpret_cast<uintptr_t>(g.a) % 16 || reinterpret_cast<uintptr_t>(g.b) % 16 ||
-        reinterpret_cast<uintptr_t>(g.c) % 16 || reinterpret_cast<uintptr_t>(g.r) % 16 ||
+        reinterpret_cast<uintptr_t>(g.c) % 16 || (!loss && reinterpret_cast<uintptr_t>(g.r) % 16) ||
         reinterpret_cast<uintptr_t>(g.c2) % 16)
         return false;
     if (g.a_batch % 8 || g.b_batch % 8 || g.c_batch % 8 || g.r_batch % 8)

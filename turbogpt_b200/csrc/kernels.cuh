@@ -150,6 +150,10 @@ enum class Epilogue {
     GeluDual = 2,  // pre = round(acc); C = gelu'(pre) (kept for backward); C2 = gelu(pre)
     GeluGrad = 3,  // C = round(acc) * R, R = the saved gelu'(pre)
     Axpby = 4,     // C = alpha * acc + beta * R    (Newton-Schulz updates)
+    // 256-way softmax cross-entropy on the FP32 accumulators (reference cuda/model.cuh:31-58 fuses the head
+    // and the loss the same way; the logits never reach memory): n = 256; R = uint8 targets [m];
+    // C2 = FP32 losses [m]; C = BF16 (softmax - onehot) * alpha, or nullptr for the loss alone.
+    CrossEntropy = 5,
 };
 struct GemmArgs {
     Dtype in = Dtype::BF16, out = Dtype::BF16;
@@ -168,7 +172,10 @@ struct GemmArgs {
     int batch = 1;           // batched over z with element strides below
     int64_t a_batch = 0, b_batch = 0, c_batch = 0, r_batch = 0;
 };
-void launch_gemm_simt(const GemmArgs &g, cudaStream_t s);
+// `scratch`: gemm_simt_scratch_bytes(g) bytes for shapes that are cut along K (small outputs over a long K,
+// partial tiles added in a fixed order); nullptr: never cut.
+size_t gemm_simt_scratch_bytes(const GemmArgs &g);
+void launch_gemm_simt(const GemmArgs &g, cudaStream_t s, float *scratch = nullptr);
 // tcgen05 path; returns false when the shape/layout is outside what it supports.
 bool gemm_tc_supported(const GemmArgs &g);
 // Split-K scratch of the tcgen05 GEMM: FP32 partial tiles, one ticket per output tile (zero between

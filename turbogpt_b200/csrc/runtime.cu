@@ -306,6 +306,23 @@ int tg_ex_gemm(const void *a, int64_t a_row, int64_t a_col, const void *b, int64
         CHECK_CUDA(cudaGetLastError());
     });
 }
+int tg_ex_head_cross_entropy(const void *x, const void *head, const uint8_t *targets, float *losses, void *dlogits,
+                             int rows, int width, float scale, void *stream) {
+    return guarded([&] {
+        require_sm100();
+        if (!x || !head || !targets || !losses)
+            throw std::runtime_error("Missing head or loss operand");
+        GemmArgs g;
+        g.a = x, g.a_row = width, g.b = head, g.b_row = width, g.c = dlogits, g.ldc = Vocabulary;
+        g.m = rows, g.n = Vocabulary, g.k = width;
+        g.in = Dtype::BF16, g.out = Dtype::BF16;
+        g.epilogue = Epilogue::CrossEntropy, g.r = targets, g.c2 = losses, g.alpha = scale;
+        if (!gemm_tc_supported(g))
+            throw std::runtime_error("head + loss: width must be a multiple of 8 and at least 64, operands 16-byte aligned");
+        launch_gemm_tc(g, device_sms(), nullptr, static_cast<cudaStream_t>(stream));
+        CHECK_CUDA(cudaGetLastError());
+    });
+}
 int tg_ex_weight_gradient_static(const void *dy, const void *x, float *dw, int out, int in, int tokens,
                                  void *stream) {
     return guarded([&] {
