@@ -581,7 +581,10 @@ void Engine::muon_family(int64_t first_offset, int rows, int cols) {
     run(FMuon, [&] { launch_muon_normalize(muon_x[0], muon_sumsq, per, depth, stream); });
     bf16 *cur = muon_x[0] + first * per, *nxt = muon_x[1] + first * per;
     bf16 *a_buffer = muon_a + int64_t(first) * r * r, *b_buffer = muon_b + int64_t(first) * r * r;
-    for (int it = 0; it < c.base.ns_steps; ++it) {
+    const bool small = muon_newton_schulz_small_supported(r, n); // the reference architecture: one launch, in place
+    if (small)
+        run(FMuon, [&] { launch_muon_newton_schulz_small(cur, r, n, c.base.ns_steps, mine, stream); });
+    for (int it = 0; !small && it < c.base.ns_steps; ++it) {
         GemmArgs a; // A = X X^T
         a.a = cur, a.a_row = n, a.b = cur, a.b_row = n, a.c = a_buffer, a.ldc = r, a.m = r, a.n = r, a.k = n;
         a.batch = mine, a.a_batch = per, a.b_batch = per, a.c_batch = int64_t(r) * r, a.out = Dtype::BF16;

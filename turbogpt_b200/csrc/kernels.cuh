@@ -233,6 +233,9 @@ struct MuonPrepareArgs { // momentum, Nesterov direction, BF16 cast (+ transpose
 };
 void launch_muon_prepare(const MuonPrepareArgs &a, cudaStream_t s);
 void launch_muon_normalize(bf16 *x, const float *sumsq, int64_t per_matrix, int batch, cudaStream_t s);
+// `matrices` consecutive [r, n] BF16 matrices (r <= n), orthogonalised in place by `steps` Newton-Schulz iterations.
+bool muon_newton_schulz_small_supported(int r, int n);
+void launch_muon_newton_schulz_small(bf16 *x, int r, int n, int steps, int matrices, cudaStream_t s);
 struct MuonApplyArgs {
     const bf16 *x;
     bf16 *weight_high;

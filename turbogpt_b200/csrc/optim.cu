@@ -262,6 +262,57 @@ void launch_muon_normalize(bf16 *x, const float *sumsq, int64_t per_matrix, int 
     else
         muon_normalize_kernel<<<dim3(MuonBlocks, batch), 256, 0, s>>>(x, sumsq, per_matrix);
 }
+// All Newton-Schulz iterations of one small matrix (the reference architecture's 16 x 16 .. 16 x 48) in one
+// block's shared memory, with the roundings of the three-GEMM form: BF16 operands, FP32 sums over ascending k,
+// A = X X^T, B = 2.0315 A A - 4.775 A and X' = B X + 3.4445 X each rounded to BF16 (reference
+// cuda/optim.cuh:60-106).  One launch instead of three per iteration.
+__global__ void __launch_bounds__(256) muon_newton_schulz_small_kernel(bf16 *x_all, int r, int n, int steps) {
+    extern __shared__ float shared[];
+    float *x = shared, *a = x + r * n, *b = a + r * r, *next = b + r * r;
+    bf16 *matrix = x_all + int64_t(blockIdx.x) * r * n;
+    for (int i = threadIdx.x; i < r * n; i += blockDim.x)
+        x[i] = __bfloat162float(matrix[i]);
+    __syncthreads();
+    for (int step = 0; step < steps; ++step) {
+        for (int i = threadIdx.x; i < r * r; i += blockDim.x) {
+            const float *p = x + (i / r) * n, *q = x + (i % r) * n;
+            float sum = 0.f;
+            for (int k = 0; k < n; ++k)
+                sum = fmaf(p[k], q[k], sum);
+            a[i] = rounded<bf16>(sum);
+        }
+        __syncthreads();
+        for (int i = threadIdx.x; i < r * r; i += blockDim.x) {
+            const float *p = a + (i / r) * r;
+            const int column = i % r;
+            float sum = 0.f;
+            for (int k = 0; k < r; ++k)
+                sum = fmaf(p[k], a[k * r + column], sum);
+            b[i] = rounded<bf16>(2.0315f * sum + -4.775f * a[i]);
+        }
+        __syncthreads();
+        for (int i = threadIdx.x; i < r * n; i += blockDim.x) {
+            const float *p = b + (i / n) * r;
+            const int column = i % n;
+            float sum = 0.f;
+            for (int k = 0; k < r; ++k)
+                sum = fmaf(p[k], x[k * n + column], sum);
+            next[i] = rounded<bf16>(1.f * sum + 3.4445f * x[i]);
+        }
+        __syncthreads();
+        for (int i = threadIdx.x; i < r * n; i += blockDim.x)
+            x[i] = next[i];
+        __syncthreads();
+    }
+    for (int i = threadIdx.x; i < r * n; i += blockDim.x)
+        matrix[i] = __float2bfloat16(x[i]);
+}
+bool muon_newton_schulz_small_supported(int r, int n) { return r <= 32 && n <= 128; }
+void launch_muon_newton_schulz_small(bf16 *x, int r, int n, int steps, int matrices, cudaStream_t s) {
+    const size_t bytes = size_t(2 * r * n + 2 * r * r) * sizeof(float); // at most 40 KB
+    muon_newton_schulz_small_kernel<<<matrices, 256, bytes, s>>>(x, r, n, steps);
+}
+
 // w = w * (1 - lr * wd) - lr * sqrt(max(1, rows/cols)) * x, x transposed back when rows > cols.
 __global__ void __launch_bounds__(256) muon_apply_kernel(MuonApplyArgs a) {
     float multiplier = 1;
