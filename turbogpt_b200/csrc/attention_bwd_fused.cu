@@ -111,13 +111,7 @@ template <int Pending> __device__ __forceinline__ void bulk_wait() {
 }
 // ... and when all of them have at least read their shared memory.
 __device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
-// Contiguous global memory -> shared memory by the copy engine (16-byte aligned, a multiple of 16 bytes); the bytes
-// count towards the barrier's phase like those of a tile load.
-__device__ __forceinline__ void bulk_load(uint32_t shared, const void *global, uint32_t bytes, uint32_t bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(shared), "l"(global),
-                 "r"(bytes), "r"(bar)
-                 : "memory");
-}
+
 // Register budget of the calling group of four warps from here on (all four execute it together).
 template <int Registers> __device__ __forceinline__ void shrink_registers() {
     asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(Registers));

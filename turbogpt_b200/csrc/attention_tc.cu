@@ -363,7 +363,9 @@ struct BackwardParams {
     const bf16 *out; // forward output, for delta = rowsum(dO * O)
     bf16 *dqkv;
     const float *lse;
-    float *delta;    // written by the dq kernel, read by the dk/dv kernel that follows it
+    // [2][batch * heads][tiles * 128]: every query's lse in base 2, then its delta, in rows padded to whole tiles
+    // (zeros in the padding); written by the dq kernel, fetched 64 at a time by the dk/dv kernel that follows it
+    float *statistics;
     int batch, context, heads, width, tiles;
     float scale, scale_log2;
     StepCounters *counters;
@@ -520,8 +522,8 @@ flash_dq_kernel(const __grid_constant__ CUtensorMap map_qkv128, const __grid_con
         const int warp_first = tile * BlockM + quarter * 32; // earliest query of this warp
         const uint32_t lane_base = tmem_base + (uint32_t(quarter * 32) << 16);
         const bool valid = position < p.context, ragged = warp_first + 31 >= p.context;
-        const int64_t stat = (int64_t(b) * p.heads + h) * p.context + position;
-        const float lse2 = valid ? p.lse[stat] * 1.4426950408889634f : 0.f;
+        const int64_t padded = int64_t(p.tiles) * BlockM, stat = bh * padded + position;
+        const float lse2 = valid ? p.lse[(int64_t(b) * p.heads + h) * p.context + position] * 1.4426950408889634f : 0.f;
         // delta = rowsum(dO * O) for this thread's query: O from global memory, dO from the tile the TMA
         // warp loaded (row r of a 128-byte-swizzled tile keeps its 16-byte chunk c at position c ^ (r % 8)).
         float delta = 0.f;
@@ -546,8 +548,10 @@ flash_dq_kernel(const __grid_constant__ CUtensorMap map_qkv128, const __grid_con
                         delta += __uint_as_float(a4[i] << 16) * __uint_as_float(b4[i] << 16) +
                                  __uint_as_float(a4[i] & 0xffff0000u) * __uint_as_float(b4[i] & 0xffff0000u);
                 }
-                if (half == 0)
-                    p.delta[stat] = delta;
+            }
+            if (ok && half == 0) { // rows past the end of the sequence hold zeros
+                p.statistics[stat] = lse2;
+                p.statistics[pairs * padded + stat] = delta;
             }
         }
         for (int j = 0; j < blocks && ok; ++j) {
@@ -676,38 +680,25 @@ flash_dkv_kernel(const __grid_constant__ CUtensorMap map_qkv128, const __grid_co
     const uint32_t tmem_dp = tmem_base + 64, tmem_dv = tmem_base + 128, tmem_dk = tmem_base + 192;
 
     if (warp == 0) {
-        // The whole warp runs the producer loop: lane 0 issues the TMA loads, every lane fetches two
-        // queries' statistics into the ring slot before lane 0's arrival releases them.
+        // One thread issues every load: the tiles by TMA and the step's 64 lse and delta values as two bulk
+        // copies from the padded rows, so nothing passes through registers and no load latency sits between steps.
         if (lane == 0) {
             mbarrier_expect_tx(kv_full, 2 * TileBytes);
             tma_load_3d(smem_k, &map_qkv128, p.width + h * HeadSize, row0 + tile * BlockN, 0, kv_full);
             tma_load_3d(smem_v, &map_qkv128, 2 * p.width + h * HeadSize, row0 + tile * BlockN, 0, kv_full);
-        }
-        const float *lse = p.lse + (int64_t(b) * p.heads + h) * p.context;
-        const float *delta = p.delta + (int64_t(b) * p.heads + h) * p.context;
-        for (int i = 0; i < blocks; ++i) {
-            const int ring = i % DkvRing, q0 = (first_block + i) * DkvStep;
-            float values[4] = {0.f, 0.f, 0.f, 0.f}; // lse2 and delta of queries q0 + lane and q0 + 32 + lane
-#pragma unroll
-            for (int u = 0; u < 2; ++u)
-                if (q0 + u * 32 + lane < p.context) {
-                    values[u] = lse[q0 + u * 32 + lane] * 1.4426950408889634f;
-                    values[2 + u] = delta[q0 + u * 32 + lane];
-                }
-            bool ok = mbarrier_wait(qdo_empty0 + 8 * ring, ((i / DkvRing) & 1) ^ 1, abort_flag, p.counters, 311);
-            if (!__all_sync(0xffffffffu, ok))
-                break;
-#pragma unroll
-            for (int u = 0; u < 2; ++u) {
-                statistics[ring * 128 + u * 32 + lane] = values[u];
-                statistics[ring * 128 + 64 + u * 32 + lane] = values[2 + u];
-            }
-            __syncwarp();
-            if (lane == 0) {
-                const uint32_t bar = qdo_full0 + 8 * ring, dst = smem_qdo + ring * 2 * DkvStepBytes;
-                mbarrier_expect_tx(bar, 2 * DkvStepBytes);
+            const int64_t padded = int64_t(p.tiles) * BlockM;
+            const float *lse2 = p.statistics + bh * padded, *delta = lse2 + pairs * padded;
+            for (int i = 0; i < blocks; ++i) {
+                const int ring = i % DkvRing, q0 = (first_block + i) * DkvStep;
+                if (!mbarrier_wait(qdo_empty0 + 8 * ring, ((i / DkvRing) & 1) ^ 1, abort_flag, p.counters, 311))
+                    break;
+                const uint32_t bar = qdo_full0 + 8 * ring, dst = smem_qdo + ring * 2 * DkvStepBytes,
+                               stats = smem_address(statistics + ring * 128);
+                mbarrier_expect_tx(bar, 2 * DkvStepBytes + 2 * DkvStep * 4);
                 tma_load_3d(dst, &map_qkv64, h * HeadSize, row0 + q0, 0, bar);
                 tma_load_3d(dst + DkvStepBytes, &map_do64, h * HeadSize, row0 + q0, 0, bar);
+                bulk_load(stats, lse2 + q0, DkvStep * 4, bar);
+                bulk_load(stats + DkvStep * 4, delta + q0, DkvStep * 4, bar);
             }
         }
     } else if (warp == 1) {
@@ -899,8 +890,12 @@ void launch_flash_attention_forward(const void *qkv, void *out, float *lse, int 
     CHECK_CUDA(cudaGetLastError());
 }
 
+size_t flash_attention_backward_scratch_bytes(int batch, int context, int heads) {
+    return size_t(2) * batch * heads * ((context + BlockM - 1) / BlockM) * BlockM * sizeof(float);
+}
+
 void launch_flash_attention_backward(const void *qkv, const void *out, const void *dout, const float *lse,
-                                     float *delta, void *dqkv, int batch, int context, int heads,
+                                     float *scratch, void *dqkv, int batch, int context, int heads,
                                      StepCounters *counters, cudaStream_t s) {
     static bool configured[64] = {};
     int device = 0;
@@ -912,7 +907,7 @@ void launch_flash_attention_backward(const void *qkv, const void *out, const voi
     }
     const int width = heads * HeadSize;
     BackwardParams p{};
-    p.out = static_cast<const bf16 *>(out), p.dqkv = static_cast<bf16 *>(dqkv), p.lse = lse, p.delta = delta;
+    p.out = static_cast<const bf16 *>(out), p.dqkv = static_cast<bf16 *>(dqkv), p.lse = lse, p.statistics = scratch;
     p.batch = batch, p.context = context, p.heads = heads, p.width = width;
     p.tiles = (context + BlockM - 1) / BlockM;
     p.scale = 1.f / sqrtf(float(HeadSize));

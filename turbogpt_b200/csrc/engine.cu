@@ -157,7 +157,9 @@ void Engine::initialize() {
     bytes(dwide, M * wide);
     bytes(dactivated, M * Hd);
     bytes(dqkv, M * 3 * W);
-    allocate(attention_scratch, M * c.heads, false);
+    allocate(attention_scratch,
+             std::max<size_t>(size_t(M) * c.heads, flash_attention_backward_scratch_bytes(c.base.batch, T, c.heads) / sizeof(float)),
+             false);
     allocate(simt_scratch, SimtScratchBytes / sizeof(float), false);
     norm_blocks = norm_backward_blocks(tokens, sms);
     allocate(norm_partial, size_t(norm_blocks) * 2 * W, false);

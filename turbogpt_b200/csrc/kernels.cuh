@@ -107,9 +107,11 @@ bool flash_attention_supported(int width, int heads);
 void launch_flash_attention_forward(const void *qkv, void *out, float *lse, int batch, int context, int heads,
                                     StepCounters *counters, cudaStream_t s);
 
-// `delta` ([batch, heads, context] floats) is scratch: the dq kernel fills it with rowsum(dout * out).
+// `scratch`: flash_attention_backward_scratch_bytes() bytes; the dq kernel fills it with every query's lse
+// (base 2) and rowsum(dout * out) for the dk/dv kernel.
+size_t flash_attention_backward_scratch_bytes(int batch, int context, int heads);
 void launch_flash_attention_backward(const void *qkv, const void *out, const void *dout, const float *lse,
-                                     float *delta, void *dqkv, int batch, int context, int heads,
+                                     float *scratch, void *dqkv, int batch, int context, int heads,
                                      StepCounters *counters, cudaStream_t s);
 
 // One fused kernel for dQ, dK and dV (attention_bwd_fused.cu): every probability is exponentiated once.

@@ -392,8 +392,8 @@ int tg_ex_attention_backward(const void *qkv, const void *out, const void *dout,
                                                   attention_scratch(flash_backward_scratch_bytes(batch, context, heads)), batch,
                                                   context, heads, nullptr, s);
         } else if (tensor_cores) { // what the engine runs: dQ by query tile, then dK and dV by key tile
-            float *delta = static_cast<float *>(attention_scratch(size_t(batch) * heads * context * sizeof(float)));
-            launch_flash_attention_backward(qkv, out, dout, lse, delta, dqkv, batch, context, heads, nullptr, s);
+            float *scratch = static_cast<float *>(attention_scratch(flash_attention_backward_scratch_bytes(batch, context, heads)));
+            launch_flash_attention_backward(qkv, out, dout, lse, scratch, dqkv, batch, context, heads, nullptr, s);
         } else {
             float *delta = static_cast<float *>(attention_scratch(size_t(batch) * heads * context * sizeof(float)));
             SoftmaxAttentionBackwardArgs a{qkv, out, dout, lse, delta, dqkv, batch, context, heads * d_head, heads};

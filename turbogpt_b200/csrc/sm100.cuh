@@ -141,6 +141,13 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *map
                  "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y), "r"(z)
                  : "memory");
 }
+// Contiguous global memory -> shared memory by the copy engine (both 16-byte aligned, a multiple of 16 bytes);
+// the bytes count towards the barrier's phase like those of a tile load.
+__device__ __forceinline__ void bulk_load(uint32_t shared, const void *global, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(shared),
+                 "l"(global), "r"(bytes), "r"(bar)
+                 : "memory");
+}
 __device__ __forceinline__ void prefetch_map(const CUtensorMap *map) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
 }
