@@ -105,7 +105,7 @@ class ClockSampler:
         self.process = None
         try:
             self.process = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "200",
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "50",
                  "-i", str(device)], stdout=self.file, stderr=subprocess.DEVNULL)
         except OSError:
             pass
@@ -376,6 +376,9 @@ def main() -> None:
         work = {"gemm_forward": f["gemm_pass"] * tokens, "gemm_input_grad": f["gemm_pass"] * tokens,
                 "gemm_weight_grad": f["gemm_pass"] * tokens, "attention_forward": f["attention_forward"] * tokens,
                 "attention_backward": 2.5 * f["attention_forward"] * tokens}
+        # the profiled leg is short: with too few samples of its own it borrows the timed region's median clock
+        if (profile_clocks.get("samples") or 0) < 4 and clocks and clocks.get("sm_mhz"):
+            profile_clocks = dict(profile_clocks, sm_mhz=clocks["sm_mhz"], borrowed_from="the timed region")
         mhz = profile_clocks.get("sm_mhz")
         for k, flop in work.items():
             if k in per_step and per_step[k]["ms"] > 0:
