@@ -411,7 +411,8 @@ def main() -> None:
             "families_ms_per_step": per_step,
         }
     if rank == 0 and not args.no_cpu_baseline and world == 1:
-        cpu_value, cores, sample = cpu_step_tokens_per_second(w, 1, 1)
+        cpu_step_tokens_per_second(w, 1, 1)  # warm-up: thread pools, allocations
+        cpu_value, cores, sample = cpu_step_tokens_per_second(w, 4, 2)  # about 15-25 s of host work
         result["cpu_baseline"] = {"value": cpu_value, "unit": "tokens/s", "cores": cores, "kind": "port",
                                   "sample": sample}
     if rank == 0:
