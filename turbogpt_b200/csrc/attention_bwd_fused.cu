@@ -2,17 +2,19 @@
 // the score blocks, so every probability is exponentiated once (a dq kernel followed by a dk/dv kernel
 // evaluates each twice and repeats the S = Q K^T and dP = dO V^T products).  Same role as the
 // reference's attention_backward loops (cuda/attention.cuh:69-106), nothing of their structure.
-// The engine runs the two-kernel form (attention_tc.cu): measured on B200, this kernel takes 420 us
-// against 349 us at 32 x 12 x 1024, 1076 against 935 at 8 x 12 x 4096, 306 against 262 at 64 x 12 x 512
+// The engine runs the two-kernel form (attention_tc.cu): measured on B200, this kernel takes 351 us
+// against 347 us at 32 x 12 x 1024, 1048 against 928 at 8 x 12 x 4096, 220 against 262 at 64 x 12 x 512
 // (both with their statistics kernels).  It is reachable through tg_ex_attention_backward for comparison.
 // Where the time goes: tensor memory (512 columns) only leaves room for 64-query steps, whose
 // 128 x 64 x 16 products re-read their 4 KB A operand from shared memory every instruction, so a step
 // moves about 150 KB through shared memory (1 200 clocks at 128 bytes per clock) for 640 clocks of tensor
-// work; a step takes 1 700 clocks; and every CTA spends about 14 000 clocks outside its steps (6 000
-// until the first products have data, and the last dQ blocks leave after the compute warps are done).
+// work; a step takes 2 000 clocks; and between two key tiles about 7 000 clocks pass (the last products,
+// the dK/dV epilogue, and the first scores and probabilities of the next tile).
 //
-// One CTA per 128 keys of one (batch, head), one CTA per SM (all 512 columns of tensor memory).
-// It walks the query blocks at or after its keys, 64 queries per step, everything transposed
+// One persistent CTA per SM (all 512 columns of tensor memory) takes key tiles of 128 keys of one
+// (batch, head) from a fixed list, long tiles first; barriers, tensor memory and the operand ring run on
+// from one tile to the next, so a tile's loads and first products overlap the previous tile's last dQ
+// blocks leaving.  For a tile it walks the query blocks at or after its keys, 64 queries per step, everything transposed
 // (thread = key row):
 //   S^T  = K Q_j^T, dP^T = V dO_j^T          -> tensor memory, two buffers each (steps alternate)
 //   P^T  = exp(S^T / sqrt(d) - lse)          -> BF16, packed over S^T in tensor memory (A operand)
@@ -25,7 +27,7 @@
 // small kernel has prepared), so no load latency sits between two steps.  Two groups of eight compute
 // warps take alternate steps, so one group's exponentials overlap the other's dS arithmetic and the
 // tensor pipe's work on the neighbouring steps; four more warps only move finished dQ blocks out of
-// tensor memory.  Registers are redistributed (setmaxnreg): 88 per compute thread, 40 for the TMA and
+// tensor memory.  Registers are redistributed (setmaxnreg): 88 per compute thread, 48 for the TMA and
 // MMA warps, the launch count (80) for the drain warps.
 //
 // dQ of a 128-query block gets a contribution from every key tile at or before it.  The
@@ -33,9 +35,10 @@
 // says tiles 0..t-1 have added theirs, then hands its block to the copy engine as bulk FP32
 // reductions onto the running sum (tile 0 stores), and advances the counter when they have completed;
 // the tile on the diagonal is the last one, adds the running sum itself and writes the BF16 result.
-// The order is fixed, so the result is the same bits on every run.  A CTA only ever waits for a CTA
-// with a lower block index, which the hardware has dispatched before it and which waits only for
-// still lower ones, so the wait cannot deadlock; it is bounded all the same.
+// The order is fixed, so the result is the same bits on every run.  A tile only ever waits for a tile
+// earlier in the list; every CTA takes its tiles in list order, so the earliest unfinished tile never
+// waits for an unfinished one and the waits cannot deadlock while all CTAs are resident; they are bounded
+// all the same.
 #include "device_utils.cuh"
 #include "sm100.cuh"
 
@@ -52,7 +55,7 @@ constexpr int Threads = 32 * (FirstComputeWarp + ComputeWarps);
 // The kernel starts with LaunchRegisters per thread (65 536 / 768 rounded down to a multiple of 8: what ptxas
 // reports; the launcher checks it).  A group of warps can only grow into registers that other groups of the
 // same CTA have released, and it waits for them without a limit, so the releases must cover the requests.
-constexpr int LaunchRegisters = 80, ControlRegisters = 40, DrainRegisters = 80, ComputeRegisters = 88;
+constexpr int LaunchRegisters = 80, ControlRegisters = 48, DrainRegisters = 80, ComputeRegisters = 88;
 static_assert(32 * (FirstDrainWarp * (LaunchRegisters - ControlRegisters) + DrainWarps * (LaunchRegisters - DrainRegisters)) >=
                   32 * ComputeWarps * (ComputeRegisters - LaunchRegisters),
               "released registers must cover the requested ones");
@@ -69,6 +72,7 @@ struct FusedParams {
     float *dq_sum;   // [batch * heads][tiles * 128 queries][64] FP32 running sums of dQ between key tiles, rows in staging order
     int *dq_count;   // [batch * heads][tiles]: key tiles that have added their share to a 128-query block
     int batch, context, heads, width, tiles;
+    int items;       // work items: tiles x batch x heads
     float scale, scale_log2;
     StepCounters *counters;
 };
@@ -119,9 +123,7 @@ template <int Registers> __device__ __forceinline__ void shrink_registers() {
 template <int Registers> __device__ __forceinline__ void grow_registers() {
     asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(Registers));
 }
-__device__ __forceinline__ void store_shared16(uint32_t address, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
-    asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(address), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
-}
+
 
 
 __global__ void __launch_bounds__(Threads, 1)
@@ -135,19 +137,29 @@ flash_backward_kernel(const __grid_constant__ CUtensorMap map_qkv128, const __gr
     const uint32_t kv_full = smem_address(barriers), qdo_full0 = kv_full + 8, qdo_empty0 = qdo_full0 + 8 * Ring,
                    s_full0 = qdo_empty0 + 8 * Ring, dp_full0 = s_full0 + 16, p_full0 = dp_full0 + 16,
                    ds_full0 = p_full0 + 16, ds_free0 = ds_full0 + 16, dq_full0 = ds_free0 + 16, dq_free0 = dq_full0 + 16,
-                   acc_done = dq_free0 + 16; // 1 + 2 Ring + 7 x 2 + 1 = 24 barriers
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(barriers + 24);
+                   acc_done = dq_free0 + 16, acc_free = acc_done + 8, kv_free = acc_free + 8; // 1 + 2 Ring + 7 x 2 + 3 barriers
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(barriers + 2 * Ring + 18);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
     const uint32_t smem_k = base, smem_v = base + TileBytes, smem_qdo = base + OffsetRing, smem_ds = base + OffsetDs;
 
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
     const int pairs = p.batch * p.heads;
-    const int tile = int(blockIdx.x / pairs); // key tile; early tiles walk the most query blocks and are dispatched first
-    const int bh = blockIdx.x % pairs, b = bh / p.heads, h = bh % p.heads;
-    const int row0 = b * p.context;
-    const int first_block = tile * (KeyTile / Step), query_blocks = (p.context + Step - 1) / Step;
-    const int blocks = (query_blocks - first_block + 1) & ~1; // an odd count gets one empty step: dQ is formed per pair of steps
-    const int supers = blocks / 2;
+    const int query_blocks = (p.context + Step - 1) / Step;
+    // The CTA walks the work items blockIdx.x, blockIdx.x + gridDim.x, ...  Item w is key tile w / pairs of
+    // (batch, head) w % pairs: early tiles walk the most query blocks and come first, and every CTA takes its
+    // items in ascending order, so the item a dQ block waits for (w - pairs) is never behind the waiting one in
+    // any CTA's list.  Barrier phases run on across items: `base` is the number of steps before the item.
+    struct Item {
+        int tile, bh, h, row0, first_block, blocks, supers;
+    };
+    auto item_of = [&](int w) {
+        Item it;
+        it.tile = w / pairs, it.bh = w % pairs, it.h = it.bh % p.heads, it.row0 = it.bh / p.heads * p.context;
+        it.first_block = it.tile * (KeyTile / Step);
+        it.blocks = (query_blocks - it.first_block + 1) & ~1; // an odd count gets one empty step: dQ is formed per pair of steps
+        it.supers = it.blocks / 2;
+        return it;
+    };
 
     grid_launch_dependents(); // the next kernel may set itself up while this one runs
     if (threadIdx.x == 32) {
@@ -171,6 +183,8 @@ flash_backward_kernel(const __grid_constant__ CUtensorMap map_qkv128, const __gr
             mbarrier_init(dq_free0 + 8 * s, DrainWarps);
         }
         mbarrier_init(acc_done, 1);
+        mbarrier_init(acc_free, ComputeWarps);
+        mbarrier_init(kv_free, 1);
         *abort_flag = 0;
         fence_barrier_init();
     }
@@ -193,23 +207,33 @@ flash_backward_kernel(const __grid_constant__ CUtensorMap map_qkv128, const __gr
         // The producer: one thread issues every load, tiles and statistics alike, so nothing passes through
         // its registers and no load latency sits between two steps.
         if (lane == 0) {
-            mbarrier_expect_tx(kv_full, 2 * TileBytes);
-            tma_load_3d(smem_k, &map_qkv128, p.width + h * HeadSize, row0 + tile * KeyTile, 0, kv_full);
-            tma_load_3d(smem_v, &map_qkv128, 2 * p.width + h * HeadSize, row0 + tile * KeyTile, 0, kv_full);
             const int64_t padded = int64_t(p.tiles) * KeyTile;
-            const float *lse2 = p.statistics + bh * padded, *delta = lse2 + pairs * padded;
-            for (int j = 0; j < blocks; ++j) {
-                const int ring = j % Ring, q0 = (first_block + j) * Step;
-                if (!mbarrier_wait(qdo_empty0 + 8 * ring, ((j / Ring) & 1) ^ 1, abort_flag, p.counters, 341))
+            bool ok = true;
+            for (int w = blockIdx.x, n = 0, base = 0; w < p.items && ok; w += gridDim.x, ++n) {
+                const Item it = item_of(w);
+                if (n > 0) // the products of the item before have finished with K and V
+                    ok = mbarrier_wait(kv_free, (n - 1) & 1, abort_flag, p.counters, 340);
+                if (!ok)
                     break;
-                const uint32_t bar = qdo_full0 + 8 * ring, dst = smem_qdo + ring * 2 * StepBytes,
-                               stats = smem_address(statistics + ring * 128);
-                mbarrier_expect_tx(bar, 2 * StepBytes + 2 * Step * 4);
-                // rows past the end of the tensor arrive as zeros; rows of the next sequence are masked by the compute warps
-                tma_load_3d(dst, &map_qkv64, h * HeadSize, row0 + q0, 0, bar);
-                tma_load_3d(dst + StepBytes, &map_do64, h * HeadSize, row0 + q0, 0, bar);
-                bulk_load(stats, lse2 + q0, Step * 4, bar);
-                bulk_load(stats + Step * 4, delta + q0, Step * 4, bar);
+                mbarrier_expect_tx(kv_full, 2 * TileBytes);
+                tma_load_3d(smem_k, &map_qkv128, p.width + it.h * HeadSize, it.row0 + it.tile * KeyTile, 0, kv_full);
+                tma_load_3d(smem_v, &map_qkv128, 2 * p.width + it.h * HeadSize, it.row0 + it.tile * KeyTile, 0, kv_full);
+                const float *lse2 = p.statistics + it.bh * padded, *delta = lse2 + pairs * padded;
+                for (int j = 0; j < it.blocks; ++j) {
+                    const int g = base + j, ring = g % Ring, q0 = (it.first_block + j) * Step;
+                    ok = mbarrier_wait(qdo_empty0 + 8 * ring, ((g / Ring) & 1) ^ 1, abort_flag, p.counters, 341);
+                    if (!ok)
+                        break;
+                    const uint32_t bar = qdo_full0 + 8 * ring, dst = smem_qdo + ring * 2 * StepBytes,
+                                   stats = smem_address(statistics + ring * 128);
+                    mbarrier_expect_tx(bar, 2 * StepBytes + 2 * Step * 4);
+                    // rows past the end of the tensor arrive as zeros; rows of the next sequence are masked by the compute warps
+                    tma_load_3d(dst, &map_qkv64, it.h * HeadSize, it.row0 + q0, 0, bar);
+                    tma_load_3d(dst + StepBytes, &map_do64, it.h * HeadSize, it.row0 + q0, 0, bar);
+                    bulk_load(stats, lse2 + q0, Step * 4, bar);
+                    bulk_load(stats + Step * 4, delta + q0, Step * 4, bar);
+                }
+                base += it.blocks;
             }
         }
       } else if (warp == 1) {
@@ -223,10 +247,11 @@ flash_backward_kernel(const __grid_constant__ CUtensorMap map_qkv128, const __gr
                            qdo_mn_desc = smem_descriptor(smem_qdo, StepBytes, 1024),
                            ds_desc = smem_descriptor(smem_ds, 16, 1024),          // one step's tile as K-major A of dK
                            ds_mn_desc = smem_descriptor(smem_ds, TileBytes, 1024); // two steps' tiles as MN-major A of dQ
-            bool ok = mbarrier_wait(kv_full, 0, abort_flag, p.counters, 342);
+            bool ok = true;
+            int base = 0; // steps before the current item (even)
             auto issue_s = [&](int j) { // S^T = K Q_j^T; the first use of ring slot j
-                const int ring = j % Ring;
-                ok = mbarrier_wait(qdo_full0 + 8 * ring, (j / Ring) & 1, abort_flag, p.counters, 343);
+                const int ring = (base + j) % Ring;
+                ok = mbarrier_wait(qdo_full0 + 8 * ring, ((base + j) / Ring) & 1, abort_flag, p.counters, 343);
                 if (!ok)
                     return;
                 tcgen05_fence_after();
@@ -238,22 +263,28 @@ flash_backward_kernel(const __grid_constant__ CUtensorMap map_qkv128, const __gr
                 tcgen05_commit(s_full0 + 8 * (j & 1));
             };
             auto issue_dp = [&](int j) { // dP^T = V dO_j^T (the slot was awaited by issue_s(j))
-                const uint64_t do_desc = descriptor_at(qdo_desc, (j % Ring) * 2 * StepBytes + StepBytes);
+                const uint64_t do_desc = descriptor_at(qdo_desc, ((base + j) % Ring) * 2 * StepBytes + StepBytes);
 #pragma unroll
                 for (int ks = 0; ks < HeadSize / 16; ++ks)
                     tcgen05_mma_bf16(tmem_dp + 64 * (j & 1), descriptor_at(v_desc, ks * 32), descriptor_at(do_desc, ks * 32),
                                      idesc_s, ks > 0);
                 tcgen05_commit(dp_full0 + 8 * (j & 1));
             };
+          for (int w = blockIdx.x, n = 0; w < p.items && ok; w += gridDim.x, ++n) {
+            const Item it = item_of(w);
+            const int blocks = it.blocks;
+            ok = mbarrier_wait(kv_full, n & 1, abort_flag, p.counters, 342);
             for (int j = 0; j < 2 && j < blocks && ok; ++j) {
                 issue_s(j);
                 if (ok)
                     issue_dp(j);
             }
             for (int j = 0; j < blocks && ok; ++j) {
-                const int ring = j % Ring, buffer = j & 1, super = j >> 1;
+                const int ring = (base + j) % Ring, buffer = j & 1, super = (base + j) >> 1; // `super` counts on across items
                 const uint64_t q_mn = descriptor_at(qdo_mn_desc, ring * 2 * StepBytes), do_mn = descriptor_at(q_mn, StepBytes);
-                ok = mbarrier_wait(p_full0 + 8 * buffer, (j >> 1) & 1, abort_flag, p.counters, 344);
+                ok = mbarrier_wait(p_full0 + 8 * buffer, super & 1, abort_flag, p.counters, 344);
+                if (ok && j == 0 && n > 0) // the compute warps have read dK and dV of the item before
+                    ok = mbarrier_wait(acc_free, (n - 1) & 1, abort_flag, p.counters, 339);
                 if (!ok)
                     break;
                 tcgen05_fence_after();
@@ -265,7 +296,7 @@ flash_backward_kernel(const __grid_constant__ CUtensorMap map_qkv128, const __gr
                     issue_s(j + 2); // into the buffer whose P^T the products above have just read
                 if (!ok)
                     break;
-                ok = mbarrier_wait(ds_full0 + 8 * buffer, (j >> 1) & 1, abort_flag, p.counters, 345);
+                ok = mbarrier_wait(ds_full0 + 8 * buffer, super & 1, abort_flag, p.counters, 345);
                 if (!ok)
                     break;
                 tcgen05_fence_after();
@@ -294,8 +325,12 @@ flash_backward_kernel(const __grid_constant__ CUtensorMap map_qkv128, const __gr
                     tcgen05_commit(ds_free0 + 8 * (super & 1)); // both dS^T tiles of the pair may be overwritten
                 }
             }
-            if (ok)
+            if (ok) {
                 tcgen05_commit(acc_done);
+                tcgen05_commit(kv_free);
+            }
+            base += blocks;
+          }
         }
       }
     } else if (warp < FirstComputeWarp) {
@@ -315,11 +350,14 @@ flash_backward_kernel(const __grid_constant__ CUtensorMap map_qkv128, const __gr
         const uint32_t lanes = uint32_t(quarter * 32) << 16;
         float *stage = reinterpret_cast<float *>(aligned + OffsetStage) + quarter * 32 * StagePitch; // this warp's 32 rows
         const int piece = lane % 16, parity = lane / 16;
+        bool ok = true;
+        for (int w = blockIdx.x, base_super = 0, n = 0; w < p.items && ok; w += gridDim.x, ++n) {
+        const Item it = item_of(w);
+        const int tile = it.tile, bh = it.bh, h = it.h, row0 = it.row0, supers = it.supers;
         const bool first = tile == 0;
         // this warp's 32 rows (8 KB) of block tile + s, contiguous, in the staging rows' own order
         auto sums_of = [&](int s) { return p.dq_sum + ((int64_t(bh) * p.tiles + tile + s) * 128 + quarter * 32) * HeadSize; };
         int *count = p.dq_count + int64_t(bh) * p.tiles + tile; // count[s]: drain warps of earlier tiles done with block tile + s
-        bool ok = true;
         auto wait_for_tiles_before = [&](int super, int seen) { // `seen`: lane 0's earlier look; bounded; false when it gave up
             seen = __shfl_sync(0xffffffffu, seen, 0);
             if (seen >= DrainWarps * tile)
@@ -352,7 +390,7 @@ flash_backward_kernel(const __grid_constant__ CUtensorMap map_qkv128, const __gr
         }
         int released = 0; // blocks 1..released have had their counters advanced (the diagonal block has none)
         for (int super = 0; super < supers && ok; ++super) {
-            const int sb = super & 1;
+            const int running = base_super + super, sb = running & 1; // tensor-memory buffers alternate across items
             const int position0 = (tile + super) * 128 + quarter * 32; // query of this warp's first row
             const bool last = super == 0;
             int seen = 0; // this block's counter, read now, looked at when the block has been staged
@@ -363,7 +401,7 @@ flash_backward_kernel(const __grid_constant__ CUtensorMap map_qkv128, const __gr
                 prefetch_l2(next);
                 prefetch_l2(next + 128);
             }
-            ok = mbarrier_wait(dq_full0 + 8 * sb, (super >> 1) & 1, abort_flag, p.counters, 347);
+            ok = mbarrier_wait(dq_full0 + 8 * sb, (running >> 1) & 1, abort_flag, p.counters, 347);
             if (!ok)
                 break;
             tcgen05_fence_after();
@@ -434,20 +472,27 @@ flash_backward_kernel(const __grid_constant__ CUtensorMap map_qkv128, const __gr
             while (ok && released < supers - 1)
                 add_release(count + ++released, 1);
         }
+        __syncwarp(); // the staging rows are free for the next item
+        base_super += supers;
+        }
     } else {
         grow_registers<ComputeRegisters>();
         // Sixteen compute warps in two groups; group g takes the steps j = g, g + 2, ...  Inside a group two
         // warps share each 32-lane quarter of tensor memory; warp `half` takes 32 of the step's 64 queries.
         const int group = (warp - FirstComputeWarp) / 8, quarter = warp % 4, half = ((warp - FirstComputeWarp) / 4) % 2;
-        const int row = quarter * 32 + lane, key = tile * KeyTile + row; // key position inside the sequence
-        const int warp_first = tile * KeyTile + quarter * 32;            // earliest key of this warp
+        const int row = quarter * 32 + lane;
         const uint32_t lanes = uint32_t(quarter * 32) << 16;
         const uint32_t t_s = tmem_st + 64 * group + lanes + half * 32, t_dp = tmem_dp + 64 * group + lanes + half * 32;
         bool ok = true;
 
+        for (int w = blockIdx.x, n = 0, base = 0; w < p.items && ok; w += gridDim.x, ++n) {
+        const Item it = item_of(w);
+        const int tile = it.tile, h = it.h, row0 = it.row0, first_block = it.first_block, blocks = it.blocks;
+        const int key = tile * KeyTile + row;                 // key position inside the sequence
+        const int warp_first = tile * KeyTile + quarter * 32; // earliest key of this warp
         for (int j = group; j < blocks && ok; j += 2) {
-            const int ring = j % Ring, super = j >> 1, use = j >> 1;
-            ok = mbarrier_wait(qdo_full0 + 8 * ring, (j / Ring) & 1, abort_flag, p.counters, 349) && // statistics
+            const int ring = (base + j) % Ring, super = (base + j) >> 1, use = super; // counted on across items
+            ok = mbarrier_wait(qdo_full0 + 8 * ring, ((base + j) / Ring) & 1, abort_flag, p.counters, 349) && // statistics
                  mbarrier_wait(s_full0 + 8 * group, use & 1, abort_flag, p.counters, 350);
             if (!ok)
                 break;
@@ -520,26 +565,41 @@ flash_backward_kernel(const __grid_constant__ CUtensorMap map_qkv128, const __gr
                 mbarrier_arrive(ds_full0 + 8 * group);
         }
         if (ok)
-            ok = mbarrier_wait(acc_done, 0, abort_flag, p.counters, 353);
+            ok = mbarrier_wait(acc_done, n & 1, abort_flag, p.counters, 353);
         if (ok) {
             tcgen05_fence_after();
             // group 0 stores dK, group 1 dV: thread = key row, 32 columns
-            bf16 *out = p.dqkv + (int64_t(row0) + key) * 3 * p.width + h * HeadSize + half * 32;
             uint32_t a[32];
             tmem_load_32x32_async((group == 0 ? tmem_dk : tmem_dv) + lanes + half * 32, a);
             tmem_wait_load(a);
-            if (key < p.context) {
-                const float factor = group == 0 ? p.scale : 1.f;
-                bf16 *target = out + (group == 0 ? p.width : 2 * p.width);
+            tcgen05_fence_before();
+            __syncwarp();
+            if (lane == 0) // the accumulators are in registers: the next item's products may overwrite them
+                mbarrier_arrive(acc_free);
+            // Out through shared memory, so that a warp's store covers eight 64-byte row pieces instead of 32
+            // different lines (thread = row would).  The staging bytes are the ones this same warp writes as dS^T
+            // of its group's first tile, which no product reads any more and nobody else ever writes.
+            const float factor = group == 0 ? p.scale : 1.f;
+            const uint32_t tile_base = smem_ds + group * TileBytes;
 #pragma unroll
-                for (int g = 0; g < 4; ++g) {
-                    float v[8];
+            for (int c = 0; c < 4; ++c)
+                store_shared16(tile_base + row * 128 + (((half * 4 + c) ^ (row & 7)) << 4),
+                               pack_bf16(__uint_as_float(a[8 * c]) * factor, __uint_as_float(a[8 * c + 1]) * factor),
+                               pack_bf16(__uint_as_float(a[8 * c + 2]) * factor, __uint_as_float(a[8 * c + 3]) * factor),
+                               pack_bf16(__uint_as_float(a[8 * c + 4]) * factor, __uint_as_float(a[8 * c + 5]) * factor),
+                               pack_bf16(__uint_as_float(a[8 * c + 6]) * factor, __uint_as_float(a[8 * c + 7]) * factor));
+            __syncwarp();
+            bf16 *target = p.dqkv + (group == 0 ? p.width : 2 * p.width) + h * HeadSize + half * 32 + (lane % 4) * 8;
 #pragma unroll
-                    for (int i = 0; i < 8; ++i)
-                        v[i] = __uint_as_float(a[g * 8 + i]) * factor;
-                    store8(target + g * 8, v);
-                }
+            for (int k = 0; k < 4; ++k) {
+                const int r = quarter * 32 + 8 * k + lane / 4, position = tile * KeyTile + r;
+                const uint4 v = load_shared16(tile_base + r * 128 + (((half * 4 + lane % 4) ^ (r & 7)) << 4));
+                if (position < p.context)
+                    *reinterpret_cast<uint4 *>(target + (int64_t(row0) + position) * 3 * p.width) = v;
             }
+            __syncwarp(); // every lane has read the staging bytes before the warp writes dS^T there again
+        }
+        base += blocks;
         }
     }
     __syncthreads();
@@ -590,9 +650,13 @@ size_t flash_backward_scratch_bytes(int batch, int context, int heads) {
 void launch_flash_attention_backward_fused(const void *qkv, const void *out, const void *dout, const float *lse, void *dqkv, void *scratch, int batch, int context, int heads,
                                            StepCounters *counters, cudaStream_t s) {
     static bool configured[64] = {};
+    static int sms[64] = {};
     int device = 0;
     CHECK_CUDA(cudaGetDevice(&device));
-    if (device < 64 && !configured[device]) {
+    if (device >= 64)
+        throw std::runtime_error("device index out of range");
+    if (!configured[device]) {
+        CHECK_CUDA(cudaDeviceGetAttribute(&sms[device], cudaDevAttrMultiProcessorCount, device));
         cudaFuncAttributes attributes{};
         CHECK_CUDA(cudaFuncGetAttributes(&attributes, flash_backward_kernel));
         if (attributes.numRegs != LaunchRegisters) // the register hand-over between warp groups is sized for this count
@@ -625,6 +689,7 @@ void launch_flash_attention_backward_fused(const void *qkv, const void *out, con
     CUtensorMap qkv128 = make_map_bf16(qkv, uint64_t(3) * width, rows, 1, uint64_t(3) * width, 0, HeadSize, 128);
     CUtensorMap qkv64 = make_map_bf16(qkv, uint64_t(3) * width, rows, 1, uint64_t(3) * width, 0, HeadSize, Step);
     CUtensorMap do64 = make_map_bf16(dout, width, rows, 1, width, 0, HeadSize, Step);
-    flash_backward_kernel<<<batch * heads * p.tiles, Threads, SharedBytes, s>>>(qkv128, qkv64, do64, p);
+    p.items = batch * heads * p.tiles;
+    flash_backward_kernel<<<std::min(p.items, sms[device]), Threads, SharedBytes, s>>>(qkv128, qkv64, do64, p);
     CHECK_CUDA(cudaGetLastError());
 }

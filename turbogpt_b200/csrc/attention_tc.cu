@@ -301,7 +301,8 @@ flash_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         const float mine_factor = reference_max == -CUDART_INF_F ? 0.f : fast_exp2((reference_max - top) * p.scale_log2);
         const float other_factor = other_max == -CUDART_INF_F ? 0.f : fast_exp2((other_max - top) * p.scale_log2);
         const float total = running_sum * mine_factor + other_sum * other_factor;
-        if (ok && *abort_flag == 0) {
+        ok = __all_sync(0xffffffffu, ok && *abort_flag == 0); // the warp stores together or not at all
+        if (ok) {
             const float inverse = 1.f / total;
             uint32_t a[32], c[32];
             // this warp's half of the columns (32 chain .. 32 chain + 31) from its own and the other accumulator;
@@ -313,24 +314,27 @@ flash_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
             tmem_wait_load(a);
             if (other_used)
                 tmem_wait_load(c);
-            if (position < p.context) {
-                bf16 *out = p.out + (int64_t(row0) + position) * p.width + h * HeadSize + chain * 32;
-                const bool mine_used = mine > 0;
+            const bool mine_used = mine > 0;
+            uint32_t packed[16];
 #pragma unroll
-                for (int g = 0; g < 4; ++g) {
-                    float v[8];
+            for (int i = 0; i < 32; i += 2) {
+                float v[2];
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        const float x = mine_used ? __uint_as_float(a[g * 8 + i]) * mine_factor : 0.f;
-                        const float y = other_used ? __uint_as_float(c[g * 8 + i]) * other_factor : 0.f;
-                        v[i] = (x + y) * inverse;
-                    }
-                    store8(out + g * 8, v);
+                for (int u = 0; u < 2; ++u) {
+                    const float x = mine_used ? __uint_as_float(a[i + u]) * mine_factor : 0.f;
+                    const float y = other_used ? __uint_as_float(c[i + u]) * other_factor : 0.f;
+                    v[u] = (x + y) * inverse;
                 }
-                if (chain == 0) // natural-log sum-exp of the scaled scores
-                    p.lse[(int64_t(b) * p.heads + h) * p.context + position] =
-                        (top * p.scale_log2 + log2f(total)) * 0.6931471805599453f;
+                packed[i / 2] = pack_bf16(v[0], v[1]);
             }
+            // through the Q tile, which no product reads any more: 2 KB per warp
+            const int first = tile * BlockM + (row & ~31);
+            store_rows_through_shared(smem_q + (warp - 2) * 2048, packed,
+                                      p.out + (int64_t(row0) + first) * p.width + h * HeadSize + chain * 32,
+                                      int64_t(p.width) * 2, p.context - first, lane);
+            if (chain == 0 && position < p.context) // natural-log sum-exp of the scaled scores
+                p.lse[(int64_t(b) * p.heads + h) * p.context + position] =
+                    (top * p.scale_log2 + log2f(total)) * 0.6931471805599453f;
         }
     }
     __syncthreads();
@@ -371,21 +375,17 @@ struct BackwardParams {
     StepCounters *counters;
 };
 
-// Eight accumulator rows x 32 columns from tensor memory, scaled, to BF16 in global memory.
-__device__ __forceinline__ void store_accumulator(uint32_t address, bf16 *out, float factor, bool write) {
-    uint32_t a[32];
+// A warp's 32 accumulator rows x 32 columns from tensor memory, scaled, to BF16 in global memory (whole
+// warp; `staging`: 2 KB of shared memory the warp may use; `first_row`: global address of row 0's first column).
+__device__ __forceinline__ void store_accumulator(uint32_t address, uint32_t staging, bf16 *first_row, int64_t row_elements,
+                                                  int valid_rows, float factor, int lane) {
+    uint32_t a[32], packed[16];
     tmem_load_32x32_async(address, a);
     tmem_wait_load(a);
-    if (write) {
 #pragma unroll
-        for (int g = 0; g < 4; ++g) {
-            float v[8];
-#pragma unroll
-            for (int i = 0; i < 8; ++i)
-                v[i] = __uint_as_float(a[g * 8 + i]) * factor;
-            store8(out + g * 8, v);
-        }
-    }
+    for (int i = 0; i < 16; ++i)
+        packed[i] = pack_bf16(__uint_as_float(a[2 * i]) * factor, __uint_as_float(a[2 * i + 1]) * factor);
+    store_rows_through_shared(staging, packed, first_row, row_elements * 2, valid_rows, lane);
 }
 
 // dq kernel.  64 keys per step.  S = Q K^T is double-buffered in tensor memory and issued two steps
@@ -605,10 +605,11 @@ flash_dq_kernel(const __grid_constant__ CUtensorMap map_qkv128, const __grid_con
         }
         if (ok)
             ok = mbarrier_wait(dq_done, 0, abort_flag, p.counters, 306);
-        if (ok) {
+        if (__all_sync(0xffffffffu, ok)) { // through the Q tile, which no product reads any more: 2 KB per warp
             tcgen05_fence_after();
-            bf16 *out = p.dqkv + (int64_t(row0) + position) * 3 * p.width + h * HeadSize + half * 32;
-            store_accumulator(tmem_dq + (uint32_t(quarter * 32) << 16) + half * 32, out, p.scale, valid);
+            bf16 *out = p.dqkv + (int64_t(row0) + warp_first) * 3 * p.width + h * HeadSize + half * 32;
+            store_accumulator(tmem_dq + (uint32_t(quarter * 32) << 16) + half * 32, smem_q + (warp - 2) * 2048, out,
+                              3 * int64_t(p.width), p.context - warp_first, p.scale, lane);
         }
     }
     __syncthreads();
@@ -844,11 +845,15 @@ flash_dkv_kernel(const __grid_constant__ CUtensorMap map_qkv128, const __grid_co
         }
         if (ok)
             ok = mbarrier_wait(acc_done, 0, abort_flag, p.counters, 316);
-        if (ok) {
+        if (__all_sync(0xffffffffu, ok)) { // through the K and V tiles, which no product reads any more: 2 KB per warp
             tcgen05_fence_after();
-            bf16 *out = p.dqkv + (int64_t(row0) + key) * 3 * p.width + h * HeadSize + half * 32;
-            store_accumulator(tmem_dk + lanes + half * 32, out + p.width, p.scale, key < p.context);
-            store_accumulator(tmem_dv + lanes + half * 32, out + 2 * p.width, 1.f, key < p.context);
+            const int first = tile * BlockN + quarter * 32; // this warp's first key
+            bf16 *out = p.dqkv + (int64_t(row0) + first) * 3 * p.width + h * HeadSize + half * 32;
+            const uint32_t staging = smem_k + (warp - 2) * 2048;
+            store_accumulator(tmem_dk + lanes + half * 32, staging, out + p.width, 3 * int64_t(p.width), p.context - first,
+                              p.scale, lane);
+            store_accumulator(tmem_dv + lanes + half * 32, staging, out + 2 * p.width, 3 * int64_t(p.width), p.context - first,
+                              1.f, lane);
         }
     }
     __syncthreads();

@@ -141,6 +141,35 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *map
                  "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y), "r"(z)
                  : "memory");
 }
+__device__ __forceinline__ uint4 load_shared16(uint32_t address) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(address) : "memory");
+    return v;
+}
+__device__ __forceinline__ void store_shared16(uint32_t address, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(address), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+// A warp's 32 rows x 32 BF16 columns (lane = row, `packed` = the lane's 64 bytes) to global memory through 2 KB of
+// shared memory owned by the warp, so that one store instruction covers eight 64-byte row pieces.  Storing with
+// lane = row makes every instruction touch 32 different lines, which was measured to hold up the SM's whole
+// load/store path (the shared-memory traffic of the other warps included).  Rows at or after `valid_rows` are
+// not written.  The 16-byte pieces of a row sit at piece ^ (row / 2 % 4): no bank conflicts either way.
+__device__ __forceinline__ void store_rows_through_shared(uint32_t staging, const uint32_t (&packed)[16], void *first_row,
+                                                          int64_t row_bytes, int valid_rows, int lane) {
+#pragma unroll
+    for (int c = 0; c < 4; ++c)
+        store_shared16(staging + lane * 64 + ((c ^ ((lane >> 1) & 3)) << 4), packed[4 * c], packed[4 * c + 1], packed[4 * c + 2],
+                       packed[4 * c + 3]);
+    __syncwarp();
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const int r = 8 * k + lane / 4, c = lane % 4;
+        const uint4 v = load_shared16(staging + r * 64 + ((c ^ ((r >> 1) & 3)) << 4));
+        if (r < valid_rows)
+            *reinterpret_cast<uint4 *>(static_cast<char *>(first_row) + r * row_bytes + c * 16) = v;
+    }
+    __syncwarp();
+}
 // Contiguous global memory -> shared memory by the copy engine (both 16-byte aligned, a multiple of 16 bytes);
 // the bytes count towards the barrier's phase like those of a tile load.
 __device__ __forceinline__ void bulk_load(uint32_t shared, const void *global, uint32_t bytes, uint32_t bar) {
