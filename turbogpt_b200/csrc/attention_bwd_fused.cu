@@ -171,7 +171,7 @@ flash_backward_kernel(const __grid_constant__ CUtensorMap map_qkv128, const __gr
         mbarrier_init(kv_full, 1);
         for (int s = 0; s < Ring; ++s) {
             mbarrier_init(qdo_full0 + 8 * s, 1);
-            mbarrier_init(qdo_empty0 + 8 * s, 2); // both issuing threads' products have read the slot
+            mbarrier_init(qdo_empty0 + 8 * s, 1);
         }
         for (int s = 0; s < 2; ++s) {
             mbarrier_init(s_full0 + 8 * s, 1);
@@ -182,9 +182,9 @@ flash_backward_kernel(const __grid_constant__ CUtensorMap map_qkv128, const __gr
             mbarrier_init(dq_full0 + 8 * s, 1);
             mbarrier_init(dq_free0 + 8 * s, DrainWarps);
         }
-        mbarrier_init(acc_done, 2); // dV by one issuing thread, dK by the other
+        mbarrier_init(acc_done, 1);
         mbarrier_init(acc_free, ComputeWarps);
-        mbarrier_init(kv_free, 2);
+        mbarrier_init(kv_free, 1);
         *abort_flag = 0;
         fence_barrier_init();
     }
@@ -238,12 +238,15 @@ flash_backward_kernel(const __grid_constant__ CUtensorMap map_qkv128, const __gr
         }
       } else if (warp == 1) {
         if (elect_one()) {
-            // The first issuing thread: the score products S^T and dP^T, and dV += P^T dO_j.
             const uint32_t idesc_s = instruction_descriptor(KeyTile, Step, 0, 0);      // K-major x K-major
-            const uint32_t idesc_acc = instruction_descriptor(KeyTile, HeadSize, 0, 1); // TMEM A x MN-major B
+            const uint32_t idesc_acc = instruction_descriptor(KeyTile, HeadSize, 0, 1); // (TMEM or K-major A) x MN-major B
+            const uint32_t idesc_dq = instruction_descriptor(128, HeadSize, 1, 1);      // MN-major A x MN-major B
             const uint64_t k_desc = smem_descriptor(smem_k, 16, 1024), v_desc = smem_descriptor(smem_v, 16, 1024),
+                           k_mn_desc = smem_descriptor(smem_k, TileBytes, 1024),
                            qdo_desc = smem_descriptor(smem_qdo, 16, 1024),
-                           qdo_mn_desc = smem_descriptor(smem_qdo, StepBytes, 1024);
+                           qdo_mn_desc = smem_descriptor(smem_qdo, StepBytes, 1024),
+                           ds_desc = smem_descriptor(smem_ds, 16, 1024),          // one step's tile as K-major A of dK
+                           ds_mn_desc = smem_descriptor(smem_ds, TileBytes, 1024); // two steps' tiles as MN-major A of dQ
             bool ok = true;
             int base = 0; // steps before the current item (even)
             auto issue_s = [&](int j) { // S^T = K Q_j^T; the first use of ring slot j
@@ -297,9 +300,30 @@ flash_backward_kernel(const __grid_constant__ CUtensorMap map_qkv128, const __gr
                 if (!ok)
                     break;
                 tcgen05_fence_after();
-                tcgen05_commit(qdo_empty0 + 8 * ring); // this thread's products have read Q_j and dO_j
+                const uint64_t ds_tile = descriptor_at(ds_desc, ((super & 1) * 2 + buffer) * TileBytes);
+#pragma unroll
+                for (int ks = 0; ks < Step / 16; ++ks) // dK += dS^T Q_j
+                    tcgen05_mma_bf16(tmem_dk, descriptor_at(ds_tile, ks * 32), descriptor_at(q_mn, ks * 2048), idesc_acc,
+                                     (j > 0 || ks > 0) ? 1u : 0u);
+                tcgen05_commit(qdo_empty0 + 8 * ring); // Q_j and dO_j are no longer read
                 if (j + 2 < blocks)
                     issue_dp(j + 2); // the compute warps have read dP^T of step j (they wrote its dS^T)
+                if (buffer == 1) {
+                    // dQ of the pair of steps: (dS^T)^T [128 queries x 128 keys] K [128 keys x 64]
+                    if (super >= 2) {
+                        ok = mbarrier_wait(dq_free0 + 8 * (super & 1), ((super >> 1) & 1) ^ 1, abort_flag, p.counters, 346);
+                        if (!ok)
+                            break;
+                        tcgen05_fence_after();
+                    }
+                    const uint64_t ds_pair = descriptor_at(ds_mn_desc, (super & 1) * 2 * TileBytes);
+#pragma unroll
+                    for (int ks = 0; ks < KeyTile / 16; ++ks)
+                        tcgen05_mma_bf16(tmem_dq + 64 * (super & 1), descriptor_at(ds_pair, ks * 2048),
+                                         descriptor_at(k_mn_desc, ks * 2048), idesc_dq, ks > 0);
+                    tcgen05_commit(dq_full0 + 8 * (super & 1));
+                    tcgen05_commit(ds_free0 + 8 * (super & 1)); // both dS^T tiles of the pair may be overwritten
+                }
             }
             if (ok) {
                 tcgen05_commit(acc_done);
@@ -307,63 +331,6 @@ flash_backward_kernel(const __grid_constant__ CUtensorMap map_qkv128, const __gr
             }
             base += blocks;
           }
-        }
-      } else if (warp == 2) {
-        // The second issuing thread: dK += dS^T Q_j every step and dQ = dS K every second step.  One thread
-        // issuing all twenty products of a step was busy for the whole step (a small product costs its issuer
-        // 40-80 clocks); the two threads sit on different schedulers and work side by side.  A commit covers
-        // the issuing thread's own products only, so the barriers that guard operands both threads' products
-        // read (the ring slots, K and V, the accumulators) count two arrivals.
-        if (elect_one()) {
-            const uint32_t idesc_acc = instruction_descriptor(KeyTile, HeadSize, 0, 1); // K-major A x MN-major B
-            const uint32_t idesc_dq = instruction_descriptor(128, HeadSize, 1, 1);      // MN-major A x MN-major B
-            const uint64_t k_mn_desc = smem_descriptor(smem_k, TileBytes, 1024),
-                           qdo_mn_desc = smem_descriptor(smem_qdo, StepBytes, 1024),
-                           ds_desc = smem_descriptor(smem_ds, 16, 1024),          // one step's tile as K-major A of dK
-                           ds_mn_desc = smem_descriptor(smem_ds, TileBytes, 1024); // two steps' tiles as MN-major A of dQ
-            bool ok = true;
-            int base = 0;
-            for (int w = blockIdx.x, n = 0; w < p.items && ok; w += gridDim.x, ++n) {
-                const int blocks = item_of(w).blocks;
-                ok = mbarrier_wait(kv_full, n & 1, abort_flag, p.counters, 336); // dQ reads K
-                for (int j = 0; j < blocks && ok; ++j) {
-                    const int ring = (base + j) % Ring, buffer = j & 1, super = (base + j) >> 1;
-                    const uint64_t q_mn = descriptor_at(qdo_mn_desc, ring * 2 * StepBytes);
-                    ok = mbarrier_wait(ds_full0 + 8 * buffer, super & 1, abort_flag, p.counters, 345);
-                    if (ok && j == 0 && n > 0) // the compute warps have read dK of the item before
-                        ok = mbarrier_wait(acc_free, (n - 1) & 1, abort_flag, p.counters, 337);
-                    if (!ok)
-                        break;
-                    tcgen05_fence_after();
-                    const uint64_t ds_tile = descriptor_at(ds_desc, ((super & 1) * 2 + buffer) * TileBytes);
-#pragma unroll
-                    for (int ks = 0; ks < Step / 16; ++ks) // dK += dS^T Q_j
-                        tcgen05_mma_bf16(tmem_dk, descriptor_at(ds_tile, ks * 32), descriptor_at(q_mn, ks * 2048), idesc_acc,
-                                         (j > 0 || ks > 0) ? 1u : 0u);
-                    tcgen05_commit(qdo_empty0 + 8 * ring); // this thread's products have read Q_j
-                    if (buffer == 1) {
-                        // dQ of the pair of steps: (dS^T)^T [128 queries x 128 keys] K [128 keys x 64]
-                        if (super >= 2) {
-                            ok = mbarrier_wait(dq_free0 + 8 * (super & 1), ((super >> 1) & 1) ^ 1, abort_flag, p.counters, 346);
-                            if (!ok)
-                                break;
-                            tcgen05_fence_after();
-                        }
-                        const uint64_t ds_pair = descriptor_at(ds_mn_desc, (super & 1) * 2 * TileBytes);
-#pragma unroll
-                        for (int ks = 0; ks < KeyTile / 16; ++ks)
-                            tcgen05_mma_bf16(tmem_dq + 64 * (super & 1), descriptor_at(ds_pair, ks * 2048),
-                                             descriptor_at(k_mn_desc, ks * 2048), idesc_dq, ks > 0);
-                        tcgen05_commit(dq_full0 + 8 * (super & 1));
-                        tcgen05_commit(ds_free0 + 8 * (super & 1)); // both dS^T tiles of the pair may be overwritten
-                    }
-                }
-                if (ok) {
-                    tcgen05_commit(acc_done);
-                    tcgen05_commit(kv_free);
-                }
-                base += blocks;
-            }
         }
       }
     } else if (warp < FirstComputeWarp) {
