@@ -492,6 +492,7 @@ void Engine::backward() {
         NormBackwardArgs a{c.norm, xin, dy, weight_high + scale, weight_low + scale, residual, dx, norm_partial,
                            gradient + scale, layer_norm ? gradient + bias : nullptr, M, W, norm_blocks, stats};
         run(FNormBackward, [&] { launch_norm_backward(act, a, stream); });
+        ++launches; // rows kernel + reduce kernel
     };
     void *dh = dhidden[0], *dh_other = dhidden[1];
     // From the first bucket to the end of backward a collective may be running beside the GEMMs.
@@ -541,6 +542,7 @@ void Engine::backward() {
                 if (tensor_cores && act == Dtype::BF16 && flash_attention_supported(W, H)) {
                     launch_flash_attention_backward(a.qkv, a.attended, dbranch, a.lse, attention_scratch, dqkv, B, T, H,
                                                     counters, stream);
+                    ++launches; // dq kernel + dk/dv kernel
                 } else {
                     launch_softmax_attention_backward(act, at, stream);
                 }
@@ -559,6 +561,8 @@ void Engine::backward() {
         launch_embedding_backward(act, dh, x, gradient + layout.embedding, M, W, c.tied != 0, embedding_partial,
                                   stream);
     });
+    if (embedding_partial)
+        ++launches; // slices kernel + sum kernel
     exchange_bucket(layout.embedding, layout.embedding + int64_t(Vocabulary) * W, depth + 1);
     finish_exchange();
 }
