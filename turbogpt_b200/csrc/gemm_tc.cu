@@ -49,6 +49,7 @@ struct TcParams {
     int epilogue, out_fp32;
     int stages;             // depth of the operand ring
     int wide;               // C, C2 and R rows are 32-byte aligned: 256-bit epilogue accesses
+    int reduce_later;       // K splits only write their partial tiles; splitk_reduce_kernel adds them afterwards
     void *c, *c2;
     const void *r;
     long long ldc, ldr, c_batch, r_batch;
@@ -516,6 +517,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     else
                         mbarrier_arrive(tempty0 + 8 * buffer);
                 }
+                if (p.reduce_later) { // many splits: one SM adding them all would take longer than the products
+                    if (++buffer == 2) {
+                        buffer = 0;
+                        buffer_phase ^= 1;
+                    }
+                    continue;
+                }
                 // Ticket: the split that arrives last reduces the tile in split order.
                 __threadfence();
                 asm volatile("bar.sync 1, 512;" ::: "memory");
@@ -582,6 +590,52 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     } else {
         if (warp == 1)
             tmem_dealloc(tmem_base, TmemColumns);
+    }
+}
+
+// C = the K splits' partial tiles added in split order, for schedules with four or more splits: there the last
+// arriver of a tile would pull every partial tile through one SM (1 MB per CTA at eight splits: 24 000 clocks
+// at the SM's L2 read rate, as long as the products themselves); this kernel spreads the same additions, in the
+// same order, over the whole GPU.  One block per 32 x 32 chunk of the padded output (a chunk is stored column
+// by column, see the kernel above); rows go out whole through a padded shared-memory tile.
+template <bool OutFp32>
+__global__ void __launch_bounds__(256) splitk_reduce_kernel(TcParams p, long long padded_m, long long padded_n) {
+    __shared__ float tile[32][33];
+    const long long chunks_per_row = padded_n / 32, chunks_per_matrix = (padded_m / 32) * chunks_per_row;
+    const long long chunk = blockIdx.x % chunks_per_matrix;
+    const int z = int(blockIdx.x / chunks_per_matrix);
+    const long long split_stride = (long long)p.batch * padded_m * padded_n;
+    const float *source = p.workspace + (long long)z * padded_m * padded_n + chunk * 1024;
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+        const int e = threadIdx.x + 256 * u; // column e / 32, row e % 32 of the chunk
+        float sum = 0.f;
+        for (int split = 0; split < p.splits; ++split)
+            sum += __ldcg(source + split * split_stride + e);
+        tile[e / 32][e % 32] = sum;
+    }
+    __syncthreads();
+    const long long row = chunk / chunks_per_row * 32 + threadIdx.x / 8;
+    const int column = int(chunk % chunks_per_row) * 32 + (threadIdx.x % 8) * 4;
+    if (row >= p.m || column >= p.n)
+        return;
+    float v[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+        v[i] = tile[(threadIdx.x % 8) * 4 + i][threadIdx.x / 8];
+    const long long index = z * p.c_batch + row * p.ldc + column;
+    if (column + 4 <= p.n && p.wide) {
+        if constexpr (OutFp32)
+            *reinterpret_cast<float4 *>((float *)p.c + index) = make_float4(v[0], v[1], v[2], v[3]);
+        else
+            *reinterpret_cast<uint2 *>((bf16 *)p.c + index) = make_uint2(pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]));
+    } else {
+        for (int i = 0; i < 4 && column + i < p.n; ++i) {
+            if constexpr (OutFp32)
+                ((float *)p.c)[index + i] = v[i];
+            else
+                ((bf16 *)p.c)[index + i] = __float2bfloat16(v[i]);
+        }
     }
 }
 
@@ -689,6 +743,7 @@ void launch_schedule(const GemmArgs &g, const Schedule &sc, int sms, float *part
     p.b_mn = g.b_col == 1 ? 0 : 1;
     p.epilogue = int(g.epilogue), p.out_fp32 = g.out == Dtype::FP32;
     p.bn = sc.bn, p.splits = sc.splits, p.k_blocks_per_split = sc.k_blocks_per_split;
+    p.reduce_later = sc.splits >= 4; // K is only split for plain stores
     const int64_t lda = p.a_mn ? g.a_col : g.a_row, ldb = p.b_mn ? g.b_col : g.b_row;
     const int unit = sc.pair ? 2 : 1;
     const int m_tiles = (g.m + BM - 1) / BM, padded_m_tiles = (m_tiles + unit - 1) / unit * unit;
@@ -771,6 +826,15 @@ void launch_schedule(const GemmArgs &g, const Schedule &sc, int sms, float *part
     else
         launch_kind(std::false_type{});
     CHECK_CUDA(cudaGetLastError());
+    if (p.reduce_later) {
+        const long long padded_m = (long long)padded_m_tiles * BM, padded_n = (long long)n_tiles * p.bn;
+        const unsigned blocks = unsigned(padded_m / 32 * (padded_n / 32) * g.batch);
+        if (p.out_fp32)
+            splitk_reduce_kernel<true><<<blocks, 256, 0, s>>>(p, padded_m, padded_n);
+        else
+            splitk_reduce_kernel<false><<<blocks, 256, 0, s>>>(p, padded_m, padded_n);
+        CHECK_CUDA(cudaGetLastError());
+    }
 }
 } // namespace
 
