@@ -297,7 +297,7 @@ void Engine::gemm(Family f, GemmArgs g) {
     g.in = act;
     run(f, [&] {
         if (tensor_cores && gemm_tc_supported(g))
-            launch_gemm_tc(g, gemm_sms, counters, stream, &gemm_workspace);
+            launches += launch_gemm_tc(g, gemm_sms, counters, stream, &gemm_workspace) - 1;
         else
             launch_gemm_simt(g, stream, gemm_simt_scratch_bytes(g) <= SimtScratchBytes ? simt_scratch : nullptr);
     });
@@ -609,7 +609,7 @@ void Engine::muon_family(int64_t first_offset, int rows, int cols) {
             run(FMuon, [&] {
                 g->in = Dtype::BF16;
                 if (tensor_cores && gemm_tc_supported(*g))
-                    launch_gemm_tc(*g, sms, counters, stream, &gemm_workspace);
+                    launches += launch_gemm_tc(*g, sms, counters, stream, &gemm_workspace) - 1;
                 else
                     launch_gemm_simt(*g, stream);
             });

@@ -883,9 +883,10 @@ void release_gemm_workspace(GemmWorkspace &w) {
 // `workspace`: the caller's own split-K scratch (an Engine's: grown here, outside stream capture,
 // when a schedule needs more); nullptr: the per-device workspace shared by the stand-alone calls,
 // whose device-side give-ups are reported by gemm_tc_take_device_error().
-void launch_gemm_tc(const GemmArgs &g, int sms, StepCounters *counters, cudaStream_t s, GemmWorkspace *workspace) {
+int launch_gemm_tc(const GemmArgs &g, int sms, StepCounters *counters, cudaStream_t s, GemmWorkspace *workspace) {
     const Schedule sc = choose_schedule(g, sms);
     launch_with(g, sc, sms, counters, s, workspace);
+    return sc.splits >= 4 ? 2 : 1; // the product kernel, and the kernel that adds many splits' partial tiles
 }
 
 namespace {

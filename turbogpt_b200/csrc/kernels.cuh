@@ -192,7 +192,8 @@ struct GemmWorkspace {
     uint64_t generation = 1;
 };
 void release_gemm_workspace(GemmWorkspace &w);
-void launch_gemm_tc(const GemmArgs &g, int sms, StepCounters *counters, cudaStream_t s,
+// Returns the number of kernels it launched.
+int launch_gemm_tc(const GemmArgs &g, int sms, StepCounters *counters, cudaStream_t s,
                     GemmWorkspace *workspace = nullptr);
 int gemm_tc_shared_bytes();
 int gemm_tc_take_device_error(cudaStream_t s);
