@@ -38,7 +38,8 @@ LAYOUTS = [(False, False), (False, True), (True, True), (True, False)]
 
 @pytest.mark.parametrize("a_mn,b_mn", LAYOUTS)
 @pytest.mark.parametrize("m,n,k", [(128, 64, 64), (256, 256, 128), (384, 192, 320), (1000, 264, 200),
-                                   (128, 768, 4096), (4096, 2304, 768)])
+                                   (128, 768, 4096), (4096, 2304, 768),
+                                   (200, 136, 8192)])  # ragged edges with many K splits (added by their own kernel)
 def test_tensor_core_gemm_matches_fp32_product(a_mn, b_mn, m, n, k):
     lib = load_library()
     if a_mn and m % 8:
