@@ -17,9 +17,11 @@
 // (residual, saved GELU derivative, or the Newton-Schulz operand) and writes 32-byte pieces with
 // 256-bit stores.
 //
-// Weight-gradient GEMMs have few output tiles and a very long K; they are split along K, each
-// split writes an FP32 partial tile to a workspace and the last split to finish a tile (an
-// atomic ticket, no spinning) sums the partials in split order, so results are deterministic.
+// Weight-gradient GEMMs have few output tiles and a very long K; they are split along K and each
+// split writes an FP32 partial tile to a workspace.  With two or three splits the last one to finish
+// a tile (an atomic ticket, no spinning) sums the partials in split order; with four or more a second
+// kernel adds them, in the same order, over the whole GPU.  Results are deterministic either way.
+// The head GEMM has an epilogue of its own: 256-way softmax cross-entropy on the FP32 accumulators.
 #include "device_utils.cuh"
 #include "sm100.cuh"
 #include <cstdio>
